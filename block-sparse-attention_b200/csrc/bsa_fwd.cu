@@ -1,0 +1,768 @@
+// Block-sparse attention forward for sm_100a: TMA gathers of the K/V blocks named by the q2k index,
+// tcgen05 QK^T and PV MMAs accumulating in tensor memory, online softmax with LSE.
+//
+// One persistent CTA per SM walks (q tile, split) work items.  Warp roles:
+//   warps 0-3  softmax group 0: owns stream 0 (KV iterations 0, 2, 4, ...), one thread per query row
+//   warps 4-7  softmax group 1: owns stream 1 (KV iterations 1, 3, 5, ...)
+//   warp  8    MMA issue (one lane)
+//   warp  9    TMA producer (one lane)
+// Tensor memory (512 columns): S0 @0, S1 @128, O0 @256, O1 @384 (fp32, 128 lanes x 128 columns each);
+// the probabilities P_s overwrite the head of S_s (bf16: 64 columns, e4m3: 32 columns) and are the
+// A operand of the PV MMA straight from tensor memory.  The two streams keep independent running
+// (max, sum, O) and are merged once per tile in the epilogue.
+//
+// A "KV iteration" is one 128-token tile: one 128-block, or two gathered 64-blocks (the second may be a
+// masked phantom when the count is odd).  With 64-token blocks the query tile has 64 rows and sits in
+// the top half of the 128-row MMA; lanes 64-127 compute on stale shared memory and are never read.
+//
+// Semantics follow the reference kernels csrc/fwd/sm100_blk128/bsa_fwd_sm100.py (load order :953-982,
+// softmax rules csrc/utils/softmax.py:102-192, merge and LSE :1551-1636) and
+// csrc/fwd/sm100_blk64/bsa_fwd_sm100.py; the Sage FP8 scale handling follows
+// csrc/fwd/sm100_blk128/bsa_fwd_sm100_fp8_fused_pv.py:1510-1663.
+#include "../../include/bsa_b200.h"
+#include "bsa_common.cuh"
+#include "bsa_host.h"
+
+namespace bsa {
+
+struct FwdParams {
+  const int32_t* __restrict__ q2k_index;
+  const int32_t* __restrict__ q2k_nums;
+  const int32_t* __restrict__ block_sizes;
+  const float* __restrict__ q_scale;
+  const float* __restrict__ k_scale;
+  const float* __restrict__ v_scale;
+  float* lse;
+  float* partial_o;
+  float* partial_lse;
+  int* status;
+  long long bs_stride_b, bs_stride_h;
+  int fixed_count, cap;
+  int B, Hq, Hkv, G, Hidx, packed;
+  int Sq, Sk, NqT, Nkv;
+  int splits;
+  int num_work;  // B * Hidx * NqT * splits
+  float scale_log2;
+};
+
+constexpr int kThreads = 320;
+constexpr int kSoftmaxThreads = 256;
+constexpr int kMmaWarp = 8;
+constexpr int kLoadWarp = 9;
+
+// barrier ids for named barriers (0 is __syncthreads)
+constexpr int kBarSoftmaxAll = 1;
+constexpr int kBarGroup0 = 2;  // +group
+
+template <bool FP8>
+struct FwdCfg {
+  static constexpr int kElt = FP8 ? 1 : 2;
+  static constexpr int kTileBytes = 128 * 128 * kElt;  // one Q / K / V tile
+  static constexpr int kSlabs = FP8 ? 1 : 2;           // 128-byte-wide column slabs per tile
+  static constexpr int kSlabBytes = 128 * 128;         // 128 rows x 128 B
+  static constexpr int kStages = FP8 ? 8 : 5;
+  static constexpr int kOBytes = 128 * 128 * 2;  // bf16 output staging
+  static constexpr int kMmaK = FP8 ? 32 : 16;
+  static constexpr int kKSteps = 128 / kMmaK;
+  static constexpr int kPColsPerStep = FP8 ? 8 : 8;  // tensor-memory columns of P per MMA k step
+  // smem: Q | O | KV stages | barriers
+  static constexpr int kSmemBytes = kTileBytes + kOBytes + kStages * kTileBytes + 1024 /*align*/ + 512;
+};
+
+struct WorkItem {
+  int b, hidx, m, split;
+  int hkv, g;        // kv head and head offset inside the group (unpacked GQA)
+  int count;         // live entries of the q2k row
+  int it_begin, it_end;  // KV iterations of this split
+  const int32_t* row;    // q2k row
+};
+
+template <int BLK>
+__device__ __forceinline__ WorkItem decode_work(const FwdParams& p, int w) {
+  WorkItem t;
+  t.split = w % p.splits;
+  int r = w / p.splits;
+  t.m = r % p.NqT;
+  r /= p.NqT;
+  t.hidx = r % p.Hidx;
+  t.b = r / p.Hidx;
+  if (p.packed) {
+    t.hkv = t.hidx;
+    t.g = 0;
+  } else {
+    t.hkv = t.hidx / p.G;
+    t.g = t.hidx % p.G;
+  }
+  const long long row_id = ((long long)t.b * p.Hidx + t.hidx) * p.NqT + t.m;
+  int c = p.q2k_nums ? p.q2k_nums[row_id] : p.fixed_count;
+  c = max(0, min(c, p.cap));
+  t.count = c;
+  t.row = p.q2k_index + row_id * p.cap;
+  constexpr int kPerIt = 128 / BLK;
+  const int n_it = (c + kPerIt - 1) / kPerIt;
+  t.it_begin = (int)(((long long)n_it * t.split) / p.splits);
+  t.it_end = (int)(((long long)n_it * (t.split + 1)) / p.splits);
+  return t;
+}
+
+// Valid token count of KV block j for (b, h): min(block_sizes[j], tokens physically left), >= 0.
+template <int BLK>
+__device__ __forceinline__ int block_len(const FwdParams& p, int b, int h, int j) {
+  if (j < 0 || j >= p.Nkv) return 0;
+  int lim = min(BLK, p.Sk - j * BLK);
+  if (p.block_sizes) {
+    lim = min(lim, p.block_sizes[b * p.bs_stride_b + h * p.bs_stride_h + j]);
+  }
+  return max(lim, 0);
+}
+
+template <int BLK, bool FP8, bool SPLIT>
+__global__ void __launch_bounds__(kThreads, 1)
+bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
+               const FwdParams p) {
+  using Cfg = FwdCfg<FP8>;
+  constexpr int NS = Cfg::kStages;
+  constexpr int kPerIt = 128 / BLK;
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sO = sQ + Cfg::kTileBytes;
+  uint8_t* sKV = sO + Cfg::kOBytes;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + NS * Cfg::kTileBytes);
+  // barrier slots
+  //  0: q_full  1: q_empty  2..2+NS: kv_full  2+NS..2+2NS: kv_empty
+  //  then s_full[2], p_full[2], o_final
+  const uint32_t bar_base = smem_u32(bars);
+  auto BAR = [&](int i) { return bar_base + (uint32_t)i * 8u; };
+  constexpr int kQFull = 0, kQEmpty = 1, kKvFull = 2, kKvEmpty = 2 + NS, kSFull = 2 + 2 * NS,
+                kPFull = kSFull + 2, kOFinal = kPFull + 2, kNumBars = kOFinal + 1;
+  __shared__ uint32_t s_tmem_base;
+  __shared__ int s_abort;
+  __shared__ float2 s_stats[2][128];
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  WaitCtx wctx{&s_abort, p.status};
+
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    mbar_init(BAR(kQFull), 1);
+    mbar_init(BAR(kQEmpty), 1);
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(BAR(kKvFull + i), 1);
+      mbar_init(BAR(kKvEmpty + i), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(BAR(kSFull + s), 1);
+      mbar_init(BAR(kPFull + s), 128);
+    }
+    mbar_init(BAR(kOFinal), 1);
+    mbar_fence_init();
+    fence_proxy_async_smem();
+  }
+  static_assert(kNumBars <= 32, "barrier slots");
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(&s_tmem_base), 512);
+    tmem_relinquish();
+  }
+  if (warp == kLoadWarp && lane == 0) {
+    tma_prefetch_desc(&tm_q);
+    tma_prefetch_desc(&tm_k);
+    tma_prefetch_desc(&tm_v);
+    if (!SPLIT) tma_prefetch_desc(&tm_o);
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem_base;
+  const uint32_t tS[2] = {tmem + 0u, tmem + 128u};
+  const uint32_t tO[2] = {tmem + 256u, tmem + 384u};
+
+  const int seq_per_tile = p.packed ? (BLK / p.G) : BLK;  // sequence positions covered by one q tile
+
+  if (warp == kLoadWarp) {
+    // ======================================= TMA producer =======================================
+    uint32_t kv_cnt = 0;  // stages produced so far
+    uint32_t q_cnt = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < p.num_work && ok; w += gridDim.x) {
+      const WorkItem t = decode_work<BLK>(p, w);
+      const int n_it = t.it_end - t.it_begin;
+      if (n_it <= 0) continue;
+      // Q tile
+      ok = mbar_wait(BAR(kQEmpty), (q_cnt & 1) ^ 1, wctx, 100);
+      if (!ok) break;
+      if (lane == 0) {
+        // a 64-row query tile fills only the top half of each slab
+        mbar_arrive_expect_tx(BAR(kQFull), Cfg::kSlabs * BLK * 128);
+#pragma unroll
+        for (int sl = 0; sl < Cfg::kSlabs; ++sl) {
+          tma_load_5d(smem_u32(sQ + sl * Cfg::kSlabBytes), &tm_q, BAR(kQFull), sl * (128 / Cfg::kElt),
+                      t.g, t.m * seq_per_tile, t.hkv, t.b);
+        }
+      }
+      ++q_cnt;
+
+      // K/V tiles in MMA consumption order: K0, K1, V0, K2, V1, ..., K(n-1), V(n-2), V(n-1)
+      auto issue_tile = [&](const CUtensorMap* tm, int blk0, int blk1) -> bool {
+        const uint32_t stage = kv_cnt % NS;
+        const uint32_t ph = (kv_cnt / NS) & 1;
+        if (!mbar_wait(BAR(kKvEmpty + stage), ph ^ 1, wctx, 101)) return false;
+        if (lane == 0) {
+          uint8_t* dst = sKV + stage * Cfg::kTileBytes;
+          mbar_arrive_expect_tx(BAR(kKvFull + stage), Cfg::kTileBytes);
+#pragma unroll
+          for (int sl = 0; sl < Cfg::kSlabs; ++sl) {
+            const int c0 = sl * (128 / Cfg::kElt);
+            if (BLK == 128) {
+              tma_load_4d(smem_u32(dst + sl * Cfg::kSlabBytes), tm, BAR(kKvFull + stage), c0,
+                          blk0 * 128, t.hkv, t.b);
+            } else {
+              tma_load_4d(smem_u32(dst + sl * Cfg::kSlabBytes), tm, BAR(kKvFull + stage), c0,
+                          blk0 * 64, t.hkv, t.b);
+              tma_load_4d(smem_u32(dst + sl * Cfg::kSlabBytes + 64 * 128), tm, BAR(kKvFull + stage),
+                          c0, blk1 * 64, t.hkv, t.b);
+            }
+          }
+        }
+        ++kv_cnt;
+        return true;
+      };
+      // block ids of KV iteration `it` (relative to the row start)
+      auto fetch = [&](int it, int& j0, int& j1) {
+        if (BLK == 128) {
+          j0 = t.row[it];
+          j1 = j0;
+        } else {
+          j0 = t.row[2 * it];
+          j1 = (2 * it + 1 < t.count) ? t.row[2 * it + 1] : j0;
+        }
+      };
+      int j0, j1, pj0, pj1;
+      fetch(t.it_begin, pj0, pj1);
+      ok = issue_tile(&tm_k, pj0, pj1);
+      for (int i = 0; i < n_it && ok; ++i) {
+        if (i + 1 < n_it) {
+          fetch(t.it_begin + i + 1, j0, j1);
+          ok = issue_tile(&tm_k, j0, j1);
+          if (!ok) break;
+        }
+        ok = issue_tile(&tm_v, pj0, pj1);
+        pj0 = j0;
+        pj1 = j1;
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    // ========================================= MMA issue ========================================
+    constexpr uint32_t kFmt = FP8 ? 0u : 1u;  // e4m3 / bf16
+    constexpr uint32_t idesc_qk = umma_idesc(kFmt, kFmt, 0, 0, 128, 128);
+    constexpr uint32_t idesc_pv = umma_idesc(kFmt, kFmt, 0, 1, 128, 128);
+    uint32_t kv_cnt = 0, q_cnt = 0;
+    uint32_t p_cnt[2] = {0, 0};
+    bool ok = true;
+    for (int w = blockIdx.x; w < p.num_work && ok; w += gridDim.x) {
+      const WorkItem t = decode_work<BLK>(p, w);
+      const int n_it = t.it_end - t.it_begin;
+      if (n_it <= 0) continue;
+      ok = mbar_wait(BAR(kQFull), q_cnt & 1, wctx, 200);
+      if (!ok) break;
+      ++q_cnt;
+      tc_fence_after();
+
+      auto issue_qk = [&](int i) -> bool {
+        const uint32_t stage = kv_cnt % NS;
+        const uint32_t ph = (kv_cnt / NS) & 1;
+        if (!mbar_wait(BAR(kKvFull + stage), ph, wctx, 201)) return false;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t a0 = smem_u32(sQ);
+          const uint32_t b0 = smem_u32(sKV + stage * Cfg::kTileBytes);
+#pragma unroll
+          for (int k = 0; k < Cfg::kKSteps; ++k) {
+            // 32 bytes of K extent per step inside a 128-byte swizzled row; bf16 tiles continue in
+            // the second slab after four steps.
+            const uint32_t off = FP8 ? (uint32_t)k * 32u
+                                     : (uint32_t)(k >> 2) * Cfg::kSlabBytes + (uint32_t)(k & 3) * 32u;
+            const uint64_t da = umma_desc_sw128(a0 + off, 0, 1024);
+            const uint64_t db = umma_desc_sw128(b0 + off, 0, 1024);
+            if (FP8) umma_f8_ss(tS[i & 1], da, db, idesc_qk, k > 0);
+            else umma_f16_ss(tS[i & 1], da, db, idesc_qk, k > 0);
+          }
+          umma_commit(BAR(kKvEmpty + stage));
+          umma_commit(BAR(kSFull + (i & 1)));
+          if (i == n_it - 1) umma_commit(BAR(kQEmpty));
+        }
+        __syncwarp();
+        ++kv_cnt;
+        return true;
+      };
+      auto issue_pv = [&](int i) -> bool {
+        const int s = i & 1;
+        const uint32_t stage = kv_cnt % NS;
+        const uint32_t ph = (kv_cnt / NS) & 1;
+        if (!mbar_wait(BAR(kKvFull + stage), ph, wctx, 202)) return false;
+        if (!mbar_wait(BAR(kPFull + s), p_cnt[s] & 1, wctx, 203)) return false;
+        ++p_cnt[s];
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t b0 = smem_u32(sKV + stage * Cfg::kTileBytes);
+#pragma unroll
+          for (int k = 0; k < Cfg::kKSteps; ++k) {
+            // V is MN-major: one k step = kMmaK token rows of 128 B; the second 64-channel slab of a
+            // bf16 tile is reached through the leading byte offset.
+            const uint64_t db = umma_desc_sw128(b0 + (uint32_t)k * (Cfg::kMmaK * 128u),
+                                                FP8 ? 0u : (uint32_t)Cfg::kSlabBytes, 1024);
+            const uint32_t a_t = tS[s] + (uint32_t)k * Cfg::kPColsPerStep;
+            if (FP8) umma_f8_ts(tO[s], a_t, db, idesc_pv, (i >= 2) || (k > 0));
+            else umma_f16_ts(tO[s], a_t, db, idesc_pv, (i >= 2) || (k > 0));
+          }
+          umma_commit(BAR(kKvEmpty + stage));
+        }
+        __syncwarp();
+        ++kv_cnt;
+        return true;
+      };
+
+      ok = issue_qk(0);
+      if (ok && n_it > 1) ok = issue_qk(1);
+      for (int i = 0; i < n_it && ok; ++i) {
+        ok = issue_pv(i);
+        if (ok && i + 2 < n_it) ok = issue_qk(i + 2);
+      }
+      if (ok && lane == 0) umma_commit(BAR(kOFinal));
+      __syncwarp();
+    }
+  } else if (warp < 8) {
+    // ===================================== softmax + epilogue ===================================
+    const int grp = warp >> 2;                 // stream owned by this group
+    const int row = threadIdx.x & 127;         // query row inside the tile = tensor-memory lane
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const bool row_active = (BLK == 128) || (row < 64);  // warp-uniform
+    uint32_t s_cnt = 0, of_cnt = 0;
+    bool ok = true;
+    const bool need_mask_meta = (p.block_sizes != nullptr) || (p.Sk % BLK != 0);
+    constexpr float kRescaleThreshold = FP8 ? 1.8073549f /* log2(448/128) */ : 8.0f;
+    constexpr float kPBias = FP8 ? 7.0f : 0.0f;
+
+    for (int w = blockIdx.x; w < p.num_work && ok; w += gridDim.x) {
+      const WorkItem t = decode_work<BLK>(p, w);
+      const int n_it = t.it_end - t.it_begin;
+      float m_cur = -INFINITY;  // running max, log2 domain (scale applied)
+      float l_sum = 0.f;        // running sum relative to m_cur
+
+      // query row -> (sequence position, head)
+      int seq, hq;
+      if (p.packed) {
+        seq = t.m * seq_per_tile + row / p.G;
+        hq = t.hkv * p.G + row % p.G;
+      } else {
+        seq = t.m * BLK + row;
+        hq = t.hidx;
+      }
+      const bool row_valid = row_active && (seq < p.Sq);
+      float q_row_scale = 1.f;
+      if (FP8) {
+        q_row_scale = row_valid ? p.q_scale[((long long)t.b * p.Hq + hq) * p.Sq + seq] : 0.f;
+      }
+
+      for (int i = grp; i < n_it && ok; i += 2) {
+        // mask metadata for this KV iteration
+        int len0 = BLK, len1 = BLK;
+        int j0 = 0;
+        if (need_mask_meta || FP8) {
+          const int it = t.it_begin + i;
+          if (BLK == 128) {
+            j0 = t.row[it];
+            len0 = block_len<BLK>(p, t.b, t.hkv, j0);
+          } else {
+            j0 = t.row[2 * it];
+            len0 = block_len<BLK>(p, t.b, t.hkv, j0);
+            len1 = (2 * it + 1 < t.count) ? block_len<BLK>(p, t.b, t.hkv, t.row[2 * it + 1]) : 0;
+          }
+        } else if (BLK == 64) {
+          const int it = t.it_begin + i;
+          len1 = (2 * it + 1 < t.count) ? BLK : 0;
+        }
+        float ksc[8];
+        if (FP8) {
+          // eight 16-token scale groups of this 128-block
+          const int ngroups = (p.Sk + 15) / 16;
+          const float* ks = p.k_scale + ((long long)t.b * p.Hkv + t.hkv) * ngroups;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const int gi = j0 * 8 + g;
+            ksc[g] = (j0 >= 0 && gi < ngroups) ? ks[gi] * (q_row_scale * p.scale_log2) : 0.f;
+          }
+        }
+
+        ok = mbar_wait(BAR(kSFull + grp), s_cnt & 1, wctx, 300 + grp);
+        if (!ok) break;
+        ++s_cnt;
+        tc_fence_after();
+        if (!row_active) {
+          // idle half of a 64-row tile: only the barrier protocol
+          tc_fence_before();
+          mbar_arrive(BAR(kPFull + grp));
+          continue;
+        }
+        float sv[128];
+        {
+          uint32_t* su = reinterpret_cast<uint32_t*>(sv);
+          tmem_ld32(tS[grp] + lane_base + 0, su + 0);
+          tmem_ld32(tS[grp] + lane_base + 32, su + 32);
+          tmem_ld32(tS[grp] + lane_base + 64, su + 64);
+          tmem_ld32(tS[grp] + lane_base + 96, su + 96);
+          tmem_wait_ld();
+        }
+        // ---- mask
+        if (BLK == 128) {
+          if (len0 < 128) {
+#pragma unroll
+            for (int c = 0; c < 128; ++c) sv[c] = (c < len0) ? sv[c] : -INFINITY;
+          }
+        } else {
+          if (len0 < 64 || len1 < 64) {
+#pragma unroll
+            for (int c = 0; c < 64; ++c) sv[c] = (c < len0) ? sv[c] : -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 64; ++c) sv[64 + c] = (c < len1) ? sv[64 + c] : -INFINITY;
+          }
+        }
+        // ---- block max in the scaled log2 domain
+        float bm;
+        if (FP8) {
+          bm = -INFINITY;
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            float gm = sv[g * 16];
+#pragma unroll
+            for (int c = 1; c < 16; ++c) gm = fmaxf(gm, sv[g * 16 + c]);
+            // -inf * 0 would be NaN for fully masked groups beyond the sequence end
+            const float scaled = (gm == -INFINITY) ? -INFINITY : gm * ksc[g];
+            bm = fmaxf(bm, scaled);
+          }
+        } else {
+          float m0 = sv[0], m1 = sv[1], m2 = sv[2], m3 = sv[3];
+#pragma unroll
+          for (int c = 4; c < 128; c += 4) {
+            m0 = fmaxf(m0, sv[c]);
+            m1 = fmaxf(m1, sv[c + 1]);
+            m2 = fmaxf(m2, sv[c + 2]);
+            m3 = fmaxf(m3, sv[c + 3]);
+          }
+          bm = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * p.scale_log2;
+        }
+        const float m_new = fmaxf(m_cur, bm);
+        const bool first = (i == grp);
+        if (first) {
+          m_cur = m_new;
+        } else {
+          const bool need = (m_new - m_cur) > kRescaleThreshold;
+          if (__any_sync(0xffffffffu, need)) {
+            const float sc = (m_new == -INFINITY) ? 1.f : ex2_approx(m_cur - m_new);
+            m_cur = m_new;
+            l_sum *= sc;
+            // rescale O_s in tensor memory (the previous PV of this stream has completed: the commit
+            // that signalled S_s was issued after it)
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              uint32_t o[32];
+              tmem_ld32(tO[grp] + lane_base + c * 32, o);
+              tmem_wait_ld();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * sc);
+              tmem_st32(tO[grp] + lane_base + c * 32, o);
+            }
+            tmem_wait_st();
+          }
+        }
+        const float m_used = (m_cur == -INFINITY) ? 0.f : m_cur;
+        const float neg_m = kPBias - m_used;
+        // ---- exponentials, row sum, P to tensor memory
+        float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+        if (FP8) {
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) {
+            uint32_t pk[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int c = c4 * 32 + e * 4;
+              const float sc = ksc[c >> 4];
+              // masked columns hold -inf; a zero scale there would make NaN, so select explicitly
+              float x0 = (sv[c] == -INFINITY) ? 0.f : ex2_approx(fmaf(sv[c], sc, neg_m));
+              float x1 = (sv[c + 1] == -INFINITY) ? 0.f : ex2_approx(fmaf(sv[c + 1], sc, neg_m));
+              float x2 = (sv[c + 2] == -INFINITY) ? 0.f : ex2_approx(fmaf(sv[c + 2], sc, neg_m));
+              float x3 = (sv[c + 3] == -INFINITY) ? 0.f : ex2_approx(fmaf(sv[c + 3], sc, neg_m));
+              a0 += x0; a1 += x1; a2 += x2; a3 += x3;
+              pk[e] = pack_e4m3x4(x0, x1, x2, x3);
+            }
+            tmem_st8(tS[grp] + lane_base + c4 * 8, pk);
+          }
+        } else {
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) {
+            uint32_t pk[16];
+#pragma unroll
+            for (int e = 0; e < 16; ++e) {
+              const int c = c4 * 32 + e * 2;
+              const float x0 = ex2_approx(fmaf(sv[c], p.scale_log2, neg_m));
+              const float x1 = ex2_approx(fmaf(sv[c + 1], p.scale_log2, neg_m));
+              if (e & 1) { a2 += x0; a3 += x1; } else { a0 += x0; a1 += x1; }
+              pk[e] = pack_bf16x2(x0, x1);
+            }
+            tmem_st16(tS[grp] + lane_base + c4 * 16, pk);
+          }
+        }
+        l_sum += (a0 + a1) + (a2 + a3);
+        tmem_wait_st();
+        tc_fence_before();
+        mbar_arrive(BAR(kPFull + grp));
+      }
+      if (!ok) break;
+
+      // ------------------------------------ tile epilogue ------------------------------------
+      if (n_it > 0) {
+        ok = mbar_wait(BAR(kOFinal), of_cnt & 1, wctx, 310 + grp);
+        if (!ok) break;
+        ++of_cnt;
+        tc_fence_after();
+      }
+      s_stats[grp][row] = make_float2(m_cur, l_sum);
+      named_bar_sync(kBarSoftmaxAll, kSoftmaxThreads);
+      const float2 st0 = s_stats[0][row];
+      const float2 st1 = s_stats[1][row];
+      const float m_all = fmaxf(st0.x, st1.x);
+      const float w0 = (st0.x == -INFINITY) ? 0.f : ex2_approx(st0.x - m_all);
+      const float w1 = (st1.x == -INFINITY) ? 0.f : ex2_approx(st1.x - m_all);
+      const float denom = st0.y * w0 + st1.y * w1;
+      const float inv = (denom > 0.f) ? (1.f / denom) : 0.f;
+      const float f0 = w0 * inv, f1 = w1 * inv;
+      const bool has0 = n_it > 0, has1 = n_it > 1;
+
+      // this group finalises output columns [64*grp, 64*grp+64)
+      float acc[64];
+#pragma unroll
+      for (int e = 0; e < 64; ++e) acc[e] = 0.f;
+      if (row_active) {
+        if (has0) {
+          uint32_t o[64];
+          tmem_ld32(tO[0] + lane_base + grp * 64, o);
+          tmem_ld32(tO[0] + lane_base + grp * 64 + 32, o + 32);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 64; ++e) acc[e] = __uint_as_float(o[e]) * f0;
+        }
+        if (has1) {
+          uint32_t o[64];
+          tmem_ld32(tO[1] + lane_base + grp * 64, o);
+          tmem_ld32(tO[1] + lane_base + grp * 64 + 32, o + 32);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 64; ++e) acc[e] = fmaf(__uint_as_float(o[e]), f1, acc[e]);
+        }
+      }
+      tc_fence_before();
+      // all reads of O0/O1 and of the stats are done: the next tile may overwrite them
+      named_bar_sync(kBarSoftmaxAll, kSoftmaxThreads);
+
+      if (FP8) {
+        const float* vs = p.v_scale + (long long)hq * 128 + grp * 64;
+#pragma unroll
+        for (int e = 0; e < 64; ++e) acc[e] *= vs[e];
+      }
+      const float lse_log2 = (denom > 0.f) ? (m_all + lg2_approx(denom) - kPBias) : -INFINITY;
+
+      if (SPLIT) {
+        if (row_valid) {
+          const long long prow = (((long long)t.split * p.B + t.b) * p.Hq + hq) * p.Sq + seq;
+          float4* dst = reinterpret_cast<float4*>(p.partial_o + prow * 128 + grp * 64);
+#pragma unroll
+          for (int e = 0; e < 16; ++e)
+            dst[e] = make_float4(acc[4 * e], acc[4 * e + 1], acc[4 * e + 2], acc[4 * e + 3]);
+          if (grp == 0) p.partial_lse[prow] = lse_log2 * kLn2;
+        }
+      } else {
+        // stage bf16 in shared memory in the 128-byte-swizzled layout the output tensor map expects
+        const bool issuer = (threadIdx.x & 127) == 0;
+        if (issuer) tma_store_wait_read<0>();
+        named_bar_sync(kBarGroup0 + grp, 128);
+        if (row_active) {
+          uint8_t* slab = sO + grp * (128 * 128);
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            uint4 v;
+            v.x = pack_bf16x2(acc[ch * 8 + 0], acc[ch * 8 + 1]);
+            v.y = pack_bf16x2(acc[ch * 8 + 2], acc[ch * 8 + 3]);
+            v.z = pack_bf16x2(acc[ch * 8 + 4], acc[ch * 8 + 5]);
+            v.w = pack_bf16x2(acc[ch * 8 + 6], acc[ch * 8 + 7]);
+            *reinterpret_cast<uint4*>(slab + row * 128 + ((ch ^ (row & 7)) << 4)) = v;
+          }
+        }
+        fence_proxy_async_smem();
+        named_bar_sync(kBarGroup0 + grp, 128);
+        if (issuer) {
+          const int cs = t.m * seq_per_tile;
+          tma_store_5d(&tm_o, smem_u32(sO + grp * (128 * 128)), grp * 64, t.g, cs, t.hkv, t.b);
+          tma_store_commit();
+        }
+        if (grp == 0 && row_valid && p.lse != nullptr) {
+          p.lse[((long long)t.b * p.Hq + hq) * p.Sq + seq] = lse_log2 * kLn2;
+        }
+      }
+    }
+    if ((threadIdx.x & 127) == 0 && !SPLIT) tma_store_wait_all<0>();
+  }
+
+  // ------------------------------------------ teardown ------------------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// =================================================================================================
+// host side
+// =================================================================================================
+
+template <int BLK, bool FP8, bool SPLIT>
+static int launch_fwd(const bsa_fwd_args& a, const FwdParams& p, const CUtensorMap& tq,
+                      const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to,
+                      int num_sms, cudaStream_t stream) {
+  using Cfg = FwdCfg<FP8>;
+  auto kern = bsa_fwd_kernel<BLK, FP8, SPLIT>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         Cfg::kSmemBytes);
+    if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "cudaFuncSetAttribute(smem): %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  const int grid = p.num_work < num_sms ? p.num_work : num_sms;
+  if (grid <= 0) return BSA_OK;
+  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, to, p);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "forward launch: %s", cudaGetErrorString(e));
+  (void)a;
+  return BSA_OK;
+}
+
+}  // namespace bsa
+
+using namespace bsa;
+
+extern "C" int bsa_fwd(const bsa_fwd_args* a, void* cuda_stream) {
+  if (!a) return set_error(BSA_ERR_INVALID, "bsa_fwd: null args");
+  if (a->blk != 64 && a->blk != 128) return set_error(BSA_ERR_INVALID, "bsa_fwd: blk must be 64 or 128");
+  if (a->D != 128) return set_error(BSA_ERR_UNSUPPORTED, "bsa_fwd: head dimension %d not built (128 only)", a->D);
+  if (a->dtype != BSA_DTYPE_BF16 && a->dtype != BSA_DTYPE_E4M3)
+    return set_error(BSA_ERR_INVALID, "bsa_fwd: unknown dtype %d", a->dtype);
+  if (a->B < 1 || a->Hq < 1 || a->Hkv < 1 || a->Sq < 1 || a->Sk < 1)
+    return set_error(BSA_ERR_INVALID, "bsa_fwd: non-positive extent");
+  if (a->Hq % a->Hkv != 0) return set_error(BSA_ERR_INVALID, "bsa_fwd: Hq %% Hkv != 0");
+  if (!a->q || !a->k || !a->v || !a->q2k_index || !a->status)
+    return set_error(BSA_ERR_INVALID, "bsa_fwd: null tensor pointer");
+  if (a->splits < 1 || a->splits > 256) return set_error(BSA_ERR_INVALID, "bsa_fwd: splits out of [1,256]");
+  if (a->splits > 1 && (!a->partial_o || !a->partial_lse))
+    return set_error(BSA_ERR_INVALID, "bsa_fwd: split run needs partial buffers");
+  if (a->splits == 1 && !a->out) return set_error(BSA_ERR_INVALID, "bsa_fwd: null out");
+  if (a->cap < 0 || a->block_sparse_num < 0) return set_error(BSA_ERR_INVALID, "bsa_fwd: negative count");
+  const bool fp8 = a->dtype == BSA_DTYPE_E4M3;
+  const int G = a->Hq / a->Hkv;
+  if (fp8 && (G != 1 || !a->q_scale || !a->k_scale || !a->v_scale))
+    return set_error(BSA_ERR_INVALID, "bsa_fwd: FP8 path needs MHA and the three scale tensors");
+  if (fp8 && a->blk != 128)
+    return set_error(BSA_ERR_UNSUPPORTED, "bsa_fwd: FP8 64-token blocks not built");
+  const int packed = a->pack_gqa != 0 && G > 1;
+  if (packed && (a->blk % G) != 0) return set_error(BSA_ERR_INVALID, "bsa_fwd: pack_gqa needs blk %% group == 0");
+
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int num_sms = bsa_num_sms(dev);
+  if (num_sms <= 0) return set_error(BSA_ERR_CUDA, "bsa_fwd: cannot query the SM count");
+
+  FwdParams p{};
+  p.q2k_index = a->q2k_index;
+  p.q2k_nums = a->q2k_nums;
+  p.block_sizes = a->block_sizes;
+  p.q_scale = a->q_scale;
+  p.k_scale = a->k_scale;
+  p.v_scale = a->v_scale;
+  p.lse = a->lse;
+  p.partial_o = a->partial_o;
+  p.partial_lse = a->partial_lse;
+  p.status = a->status;
+  p.bs_stride_b = a->bs_stride_b;
+  p.bs_stride_h = a->bs_stride_h;
+  p.fixed_count = a->block_sparse_num;
+  p.cap = a->cap;
+  p.B = a->B;
+  p.Hq = a->Hq;
+  p.Hkv = a->Hkv;
+  p.G = G;
+  p.packed = packed;
+  p.Hidx = packed ? a->Hkv : a->Hq;
+  p.Sq = a->Sq;
+  p.Sk = a->Sk;
+  const long long rows = packed ? (long long)a->Sq * G : a->Sq;
+  p.NqT = (int)((rows + a->blk - 1) / a->blk);
+  p.Nkv = (a->Sk + a->blk - 1) / a->blk;
+  p.splits = a->splits;
+  const long long work = (long long)p.B * p.Hidx * p.NqT * p.splits;
+  if (work > 0x7fffffffLL) return set_error(BSA_ERR_UNSUPPORTED, "bsa_fwd: more than 2^31 work items");
+  p.num_work = (int)work;
+  p.scale_log2 = a->softmax_scale * kLog2e;
+
+  // tensor maps.  Q and O: 5-D (D, G, S, Hkv, B) so that a packed-GQA tile (blk/G sequence positions x G
+  // heads) is one box; K and V: 4-D (D, S, Hkv, B).
+  const int elt = fp8 ? 1 : 2;
+  const CUtensorMapDataType dt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const uint32_t inner = 128 / elt;  // elements per 128-byte swizzle row
+  CUtensorMap tq, tk, tv, to;
+  {
+    uint64_t dims[5] = {128, (uint64_t)G, (uint64_t)a->Sq, (uint64_t)a->Hkv, (uint64_t)a->B};
+    uint64_t str[4] = {(uint64_t)a->q_stride[1] * elt, (uint64_t)a->q_stride[2] * elt,
+                       (uint64_t)a->q_stride[1] * G * elt, (uint64_t)a->q_stride[0] * elt};
+    uint32_t box[5] = {inner, packed ? (uint32_t)G : 1u, (uint32_t)(packed ? a->blk / G : a->blk), 1, 1};
+    int rc = make_tensor_map(&tq, dt, 5, a->q, dims, str, box, "q");
+    if (rc) return rc;
+    if (a->splits == 1) {
+      uint64_t ostr[4] = {(uint64_t)a->o_stride[1] * 2, (uint64_t)a->o_stride[2] * 2,
+                          (uint64_t)a->o_stride[1] * G * 2, (uint64_t)a->o_stride[0] * 2};
+      uint32_t obox[5] = {64, packed ? (uint32_t)G : 1u, (uint32_t)(packed ? a->blk / G : a->blk), 1, 1};
+      rc = make_tensor_map(&to, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, a->out, dims, ostr, obox, "out");
+      if (rc) return rc;
+    } else {
+      to = tq;
+    }
+  }
+  {
+    uint64_t dims[4] = {128, (uint64_t)a->Sk, (uint64_t)a->Hkv, (uint64_t)a->B};
+    uint64_t kstr[3] = {(uint64_t)a->k_stride[2] * elt, (uint64_t)a->k_stride[1] * elt,
+                        (uint64_t)a->k_stride[0] * elt};
+    uint64_t vstr[3] = {(uint64_t)a->v_stride[2] * elt, (uint64_t)a->v_stride[1] * elt,
+                        (uint64_t)a->v_stride[0] * elt};
+    uint32_t box[4] = {inner, (uint32_t)a->blk, 1, 1};
+    int rc = make_tensor_map(&tk, dt, 4, a->k, dims, kstr, box, "k");
+    if (rc) return rc;
+    rc = make_tensor_map(&tv, dt, 4, a->v, dims, vstr, box, "v");
+    if (rc) return rc;
+  }
+
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
+  const bool split = a->splits > 1;
+  if (fp8) {
+    return split ? launch_fwd<128, true, true>(*a, p, tq, tk, tv, to, num_sms, stream)
+                 : launch_fwd<128, true, false>(*a, p, tq, tk, tv, to, num_sms, stream);
+  }
+  if (a->blk == 128) {
+    return split ? launch_fwd<128, false, true>(*a, p, tq, tk, tv, to, num_sms, stream)
+                 : launch_fwd<128, false, false>(*a, p, tq, tk, tv, to, num_sms, stream);
+  }
+  return split ? launch_fwd<64, false, true>(*a, p, tq, tk, tv, to, num_sms, stream)
+               : launch_fwd<64, false, false>(*a, p, tq, tk, tv, to, num_sms, stream);
+}
