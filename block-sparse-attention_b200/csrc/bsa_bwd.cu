@@ -1,0 +1,846 @@
+// Block-sparse attention backward for sm_100a (BF16, MHA, D = 128, 128-token blocks).
+//
+// Three launches, no atomics anywhere, every accumulation in a fixed order (bit-reproducible):
+//   1. preprocess : delta[row] = sum_d O*dO, lse_log2[row] = lse*log2(e) (+inf for empty rows so that
+//                   the recomputed probabilities are exactly 0), both padded to whole 128-row tiles
+//   2. dQ kernel  : one work item per query tile, driven by the q2k index.  Per selected KV block:
+//                   S = Q K^T, dP = dO V^T, P = exp2(S*scale - lse), dS = P o (dP - delta) (bf16, staged
+//                   in shared memory), dQ += dS K.  dQ stays in tensor memory for the whole tile.
+//   3. dK/dV kernel: one work item per KV block, driven by the k2q CSR (all query groups of the block
+//                   are walked by the same CTA, so nothing has to be reduced across CTAs).  Per query
+//                   tile of the CSR row: S^T = K Q^T, dP^T = V dO^T, P^T and dS^T (bf16) go back to
+//                   tensor memory and feed dV += P^T dO and dK += dS^T Q.
+// The probabilities are recomputed in both kernels (7 GEMMs per active pair instead of the 5 of a fused
+// kernel); in exchange dQ needs no FP32 workspace, no reduce-add traffic and no post-processing pass.
+//
+// Math and rounding points follow the reference csrc/bwd/sm100_blk128/bsa_bwd_sm100.py (P and dS rounded
+// to bf16 before the dV/dK/dQ GEMMs :1766, :1808-1809; dK and dQ scaled by softmax_scale at the end
+// :1864, :2351), its preprocess csrc/bwd/bsa_bwd_preprocess.py:184-324 and its CSR walk :86-112.
+//
+// Warp roles (both kernels): warps 0-7 compute (two groups of 128 threads, thread = tensor-memory lane,
+// group g owns columns [64g, 64g+64) of the score tiles), warp 8 MMA issue, warp 9 TMA producer.
+#include "../../include/bsa_b200.h"
+#include "bsa_common.cuh"
+#include "bsa_host.h"
+
+namespace bsa {
+
+constexpr int kBwdThreads = 320;
+constexpr int kBwdMmaWarp = 8;
+constexpr int kBwdLoadWarp = 9;
+constexpr int kTile = 128 * 128 * 2;  // bytes of one bf16 128x128 tile
+constexpr int kSlab = 128 * 128;      // bytes of one 64-column slab
+
+struct BwdParams {
+  const int32_t* __restrict__ q2k_index;
+  const int32_t* __restrict__ q2k_nums;
+  const int32_t* __restrict__ csr_offsets;
+  const int32_t* __restrict__ csr_indices;
+  const float* __restrict__ lse_log2;  // [B,H,Nq*128]
+  const float* __restrict__ delta;     // [B,H,Nq*128]
+  __nv_bfloat16* dq;
+  __nv_bfloat16* dk;
+  __nv_bfloat16* dv;
+  int* status;
+  long long dq_stride[3], dk_stride[3], dv_stride[3];
+  long long idx_cap;  // entries per (b,h) of csr_indices
+  int fixed_count, cap;
+  int B, H, Sq, Sk, Nq, Nkv, G;
+  float scale_log2, softmax_scale;
+};
+
+// ------------------------------------------------------------------------------------------------
+// 1. preprocess
+// ------------------------------------------------------------------------------------------------
+// one warp per padded row; lane l holds 4 channels
+__global__ void __launch_bounds__(256)
+bwd_preprocess_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
+                      const float* __restrict__ lse, float* __restrict__ lse_log2, float* __restrict__ delta,
+                      long long os_b, long long os_h, long long os_s, long long ds_b, long long ds_h, long long ds_s,
+                      int H, int Sq, int SqPad, long long rows_pad) {
+  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows_pad) return;
+  const int lane = threadIdx.x & 31;
+  const int s = (int)(row % SqPad);
+  const long long bh = row / SqPad;
+  const int h = (int)(bh % H);
+  const long long b = bh / H;
+  float acc = 0.f;
+  float l = INFINITY;
+  if (s < Sq) {
+    const uint2 ov = *reinterpret_cast<const uint2*>(o + b * os_b + h * os_h + (long long)s * os_s + lane * 4);
+    const uint2 dv = *reinterpret_cast<const uint2*>(d_o + b * ds_b + h * ds_h + (long long)s * ds_s + lane * 4);
+    const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov);
+    const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&dv);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const float2 a = __bfloat1622float2(o2[i]);
+      const float2 c = __bfloat1622float2(d2[i]);
+      acc = fmaf(a.x, c.x, acc);
+      acc = fmaf(a.y, c.y, acc);
+    }
+    const float lv = lse[bh * Sq + s];
+    l = (lv == -INFINITY) ? INFINITY : lv * kLog2e;
+  }
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) {
+    delta[row] = acc;
+    lse_log2[row] = l;
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// shared pieces of the two main kernels
+// ------------------------------------------------------------------------------------------------
+struct BwdSmem {
+  static constexpr int kBarBytes = 256;  // 32 mbarriers
+  static constexpr int kMisc = 16;
+};
+
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+// 64 fp32 accumulator columns of one row -> bf16, scaled -> global (128 contiguous bytes)
+__device__ __forceinline__ void store_row_half(__nv_bfloat16* dst, const uint32_t* acc, float scale) {
+#pragma unroll
+  for (int ch = 0; ch < 8; ++ch) {
+    uint4 v;
+    v.x = pack_bf16x2(__uint_as_float(acc[ch * 8 + 0]) * scale, __uint_as_float(acc[ch * 8 + 1]) * scale);
+    v.y = pack_bf16x2(__uint_as_float(acc[ch * 8 + 2]) * scale, __uint_as_float(acc[ch * 8 + 3]) * scale);
+    v.z = pack_bf16x2(__uint_as_float(acc[ch * 8 + 4]) * scale, __uint_as_float(acc[ch * 8 + 5]) * scale);
+    v.w = pack_bf16x2(__uint_as_float(acc[ch * 8 + 6]) * scale, __uint_as_float(acc[ch * 8 + 7]) * scale);
+    reinterpret_cast<uint4*>(dst)[ch] = v;
+  }
+}
+
+constexpr uint32_t kIdescKK = umma_idesc(1, 1, 0, 0, 128, 128);   // A K-major, B K-major
+constexpr uint32_t kIdescKMN = umma_idesc(1, 1, 0, 1, 128, 128);  // A K-major (smem or tmem), B MN-major
+
+// D = A(smem, K-major) * B(smem, K-major)^T over the 128-deep contraction: 8 k-steps across two slabs
+__device__ __forceinline__ void mma_ss_kk(uint32_t d, uint32_t a_base, uint32_t b_base, bool acc) {
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const uint32_t off = (uint32_t)(k >> 2) * kSlab + (uint32_t)(k & 3) * 32u;
+    umma_f16_ss(d, umma_desc_sw128(a_base + off, 0, 1024), umma_desc_sw128(b_base + off, 0, 1024), kIdescKK,
+                (acc || k > 0) ? 1u : 0u);
+  }
+}
+// D (+)= A(smem, K-major [rows][contraction]) * B(smem tile [contraction rows][128 channels], MN-major)
+__device__ __forceinline__ void mma_ss_kmn(uint32_t d, uint32_t a_base, uint32_t b_base, bool acc) {
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const uint32_t aoff = (uint32_t)(k >> 2) * kSlab + (uint32_t)(k & 3) * 32u;
+    umma_f16_ss(d, umma_desc_sw128(a_base + aoff, 0, 1024),
+                umma_desc_sw128(b_base + (uint32_t)k * 2048u, kSlab, 1024), kIdescKMN, (acc || k > 0) ? 1u : 0u);
+  }
+}
+// D (+)= A(tmem bf16, two 32-column halves at a_lo / a_hi) * B(smem MN-major)
+__device__ __forceinline__ void mma_ts_kmn(uint32_t d, uint32_t a_lo, uint32_t a_hi, uint32_t b_base, bool acc) {
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const uint32_t a = (k < 4) ? (a_lo + (uint32_t)k * 8u) : (a_hi + (uint32_t)(k - 4) * 8u);
+    umma_f16_ts(d, a, umma_desc_sw128(b_base + (uint32_t)k * 2048u, kSlab, 1024), kIdescKMN,
+                (acc || k > 0) ? 1u : 0u);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// 2. dQ kernel
+// ------------------------------------------------------------------------------------------------
+// smem: Q | dO | ring of 5 tiles (K_j, V_j alternating; the V_j slot is reused for dS_j) | barriers | misc
+constexpr int kDqStages = 5;
+constexpr int kDqSmem = 2 * kTile + kDqStages * kTile + BwdSmem::kBarBytes + BwdSmem::kMisc;
+
+__global__ void __launch_bounds__(kBwdThreads, 1)
+bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+              const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const BwdParams p) {
+  constexpr int NS = kDqStages;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* sQ = smem_raw;
+  uint8_t* sdO = sQ + kTile;
+  uint8_t* sRing = sdO + kTile;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sRing + NS * kTile);
+  uint32_t& s_tmem_base = *reinterpret_cast<uint32_t*>(bars + 32);
+  volatile int& s_abort = *reinterpret_cast<volatile int*>(bars + 33);
+  if ((smem_u32(smem_raw) & 1023u) != 0) {
+    if (threadIdx.x == 0 && atomicCAS(p.status, 0, (int)kStatusBadIndex) == 0) p.status[2] = 998;
+    return;
+  }
+  const uint32_t bar_base = smem_u32(bars);
+  auto BAR = [&](int i) { return bar_base + (uint32_t)i * 8u; };
+  // q_full, q_empty, ring_full[NS], ring_empty[NS], s_full[2], dp_full, ds_full, dq_final, dq_free
+  constexpr int kQFull = 0, kQEmpty = 1, kRFull = 2, kREmpty = 2 + NS, kSFull = 2 + 2 * NS, kDpFull = kSFull + 2,
+                kDsFull = kDpFull + 1, kDqFinal = kDsFull + 1, kDqFree = kDqFinal + 1, kNumBars = kDqFree + 1;
+  static_assert(kNumBars <= 32, "barrier slots");
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  WaitCtx wctx{&s_abort, p.status};
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    mbar_init(BAR(kQFull), 1);
+    mbar_init(BAR(kQEmpty), 1);
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(BAR(kRFull + i), 1);
+      mbar_init(BAR(kREmpty + i), 1);
+    }
+    mbar_init(BAR(kSFull), 1);
+    mbar_init(BAR(kSFull + 1), 1);
+    mbar_init(BAR(kDpFull), 1);
+    mbar_init(BAR(kDsFull), 256);
+    mbar_init(BAR(kDqFinal), 1);
+    mbar_init(BAR(kDqFree), 256);
+    mbar_fence_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == kBwdMmaWarp) {
+    tmem_alloc(smem_u32(&s_tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem_base;
+  const uint32_t tS[2] = {tmem, tmem + 128u};
+  const uint32_t tdP = tmem + 256u, tdQ = tmem + 384u;
+  const int num_work = p.B * p.H * p.Nq;
+
+  auto row_count = [&](int w) {
+    int c = p.q2k_nums ? p.q2k_nums[w] : p.fixed_count;
+    return max(0, min(c, p.cap));
+  };
+
+  if (warp == kBwdLoadWarp) {
+    uint32_t r_cnt = 0, q_cnt = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+      const int n = row_count(w);
+      if (n == 0) continue;
+      const int m = w % p.Nq;
+      const int h = (w / p.Nq) % p.H;
+      const int b = w / (p.Nq * p.H);
+      const int32_t* row = p.q2k_index + (long long)w * p.cap;
+      ok = mbar_wait(BAR(kQEmpty), (q_cnt & 1) ^ 1, wctx, 400);
+      if (!ok) break;
+      ++q_cnt;
+      if (lane == 0) {
+        mbar_arrive_expect_tx(BAR(kQFull), 2 * kTile);
+        for (int sl = 0; sl < 2; ++sl) {
+          tma_load_4d(smem_u32(sQ + sl * kSlab), &tm_q, BAR(kQFull), sl * 64, m * 128, h, b);
+          tma_load_4d(smem_u32(sdO + sl * kSlab), &tm_do, BAR(kQFull), sl * 64, m * 128, h, b);
+        }
+      }
+      for (int j = 0; j < n && ok; ++j) {
+        const int blk = row[j];
+        for (int which = 0; which < 2 && ok; ++which) {
+          const uint32_t stage = r_cnt % NS, ph = (r_cnt / NS) & 1;
+          ok = mbar_wait(BAR(kREmpty + stage), ph ^ 1, wctx, 401);
+          if (!ok) break;
+          if (lane == 0) {
+            mbar_arrive_expect_tx(BAR(kRFull + stage), kTile);
+            const CUtensorMap* tm = which ? &tm_v : &tm_k;
+            for (int sl = 0; sl < 2; ++sl)
+              tma_load_4d(smem_u32(sRing + stage * kTile + sl * kSlab), tm, BAR(kRFull + stage), sl * 64, blk * 128,
+                          h, b);
+          }
+          ++r_cnt;
+        }
+      }
+    }
+  } else if (warp == kBwdMmaWarp) {
+    uint32_t r_cnt = 0, q_cnt = 0, ds_cnt = 0, free_cnt = 0;
+    bool ok = true;
+    bool first_tile = true;
+    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+      const int n = row_count(w);
+      if (n == 0) continue;
+      ok = mbar_wait(BAR(kQFull), q_cnt & 1, wctx, 410);
+      if (!ok) break;
+      ++q_cnt;
+      tc_fence_after();
+      const uint32_t base = r_cnt;  // ring position of K_0 of this tile; K_j at base+2j, V_j at base+2j+1
+      auto stage_of = [&](uint32_t pos) { return pos % NS; };
+      auto wait_full = [&](uint32_t pos) {
+        return mbar_wait(BAR(kRFull + stage_of(pos)), (pos / NS) & 1, wctx, 411);
+      };
+      auto issue_s = [&](int j) -> bool {
+        if (!wait_full(base + 2 * j)) return false;
+        tc_fence_after();
+        if (lane == 0) {
+          mma_ss_kk(tS[j & 1], smem_u32(sQ), smem_u32(sRing + stage_of(base + 2 * j) * kTile), false);
+          umma_commit(BAR(kSFull + (j & 1)));
+        }
+        __syncwarp();
+        return true;
+      };
+      auto issue_dp = [&](int j) -> bool {
+        if (!wait_full(base + 2 * j + 1)) return false;
+        tc_fence_after();
+        if (lane == 0) {
+          mma_ss_kk(tdP, smem_u32(sdO), smem_u32(sRing + stage_of(base + 2 * j + 1) * kTile), false);
+          umma_commit(BAR(kDpFull));
+        }
+        __syncwarp();
+        return true;
+      };
+      ok = issue_s(0);
+      if (ok) ok = issue_dp(0);
+      if (ok && n > 1) ok = issue_s(1);
+      for (int j = 0; j < n && ok; ++j) {
+        ok = mbar_wait(BAR(kDsFull), ds_cnt & 1, wctx, 412);  // dS_j staged, dP and S_j consumed
+        if (!ok) break;
+        ++ds_cnt;
+        if (j + 1 < n) {
+          ok = issue_dp(j + 1);
+          if (!ok) break;
+        }
+        if (j == 0 && !first_tile) {  // the previous tile's epilogue has drained dQ
+          ok = mbar_wait(BAR(kDqFree), free_cnt & 1, wctx, 413);
+          if (!ok) break;
+          ++free_cnt;
+        }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sk = stage_of(base + 2 * j), sv = stage_of(base + 2 * j + 1);
+          // dQ += dS_j (staged in the V_j slot, K-major) * K_j (MN-major view of the K tile)
+          mma_ss_kmn(tdQ, smem_u32(sRing + sv * kTile), smem_u32(sRing + sk * kTile), j > 0);
+          umma_commit(BAR(kREmpty + sk));
+          umma_commit(BAR(kREmpty + sv));
+        }
+        __syncwarp();
+        if (j + 2 < n) ok = issue_s(j + 2);
+      }
+      if (!ok) break;
+      if (lane == 0) {
+        umma_commit(BAR(kDqFinal));
+        umma_commit(BAR(kQEmpty));
+      }
+      __syncwarp();
+      r_cnt += 2 * n;
+      first_tile = false;
+    }
+  } else if (warp < 8) {
+    const int grp = warp >> 2;
+    const int row = threadIdx.x & 127;
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    uint32_t r_cnt = 0, s_cnt[2] = {0, 0}, dp_cnt = 0, fin_cnt = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+      const int n = row_count(w);
+      const int m = w % p.Nq;
+      const int h = (w / p.Nq) % p.H;
+      const int b = w / (p.Nq * p.H);
+      const int seq = m * 128 + row;
+      __nv_bfloat16* dq_row = p.dq + b * p.dq_stride[0] + h * p.dq_stride[1] + (long long)seq * p.dq_stride[2] + grp * 64;
+      if (n == 0) {
+        if (seq < p.Sq) {
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) reinterpret_cast<uint4*>(dq_row)[ch] = make_uint4(0, 0, 0, 0);
+        }
+        continue;
+      }
+      const long long srow = ((long long)b * p.H + h) * ((long long)p.Nq * 128) + seq;
+      const float lse2 = p.lse_log2[srow];
+      const float dlt = p.delta[srow];
+      const int32_t* idx_row = p.q2k_index + (long long)w * p.cap;
+      const uint32_t base = r_cnt;
+      for (int j = 0; j < n && ok; ++j) {
+        // valid kv tokens of this block (only the last physical block can be short)
+        const int blk = idx_row[j];
+        int len = p.Sk - blk * 128;
+        len = (blk < 0 || blk >= p.Nkv) ? 0 : min(len, 128);
+        // ---- phase 1: P = exp2(S*scale - lse)
+        ok = mbar_wait(BAR(kSFull + (j & 1)), s_cnt[j & 1] & 1, wctx, 420);
+        if (!ok) break;
+        ++s_cnt[j & 1];
+        tc_fence_after();
+        float pr[64];
+        {
+          uint32_t* u = reinterpret_cast<uint32_t*>(pr);
+          tmem_ld32(tS[j & 1] + lane_base + grp * 64, u);
+          tmem_ld32(tS[j & 1] + lane_base + grp * 64 + 32, u + 32);
+          tmem_wait_ld();
+        }
+        const float neg_l = -lse2;
+#pragma unroll
+        for (int c = 0; c < 64; ++c) pr[c] = ex2_approx(fmaf(pr[c], p.scale_log2, neg_l));
+        if (len < 128) {
+#pragma unroll
+          for (int c = 0; c < 64; ++c) pr[c] = (grp * 64 + c < len) ? pr[c] : 0.f;
+        }
+        // ---- phase 2: dS = P o (dP - delta) -> bf16 -> shared memory (the V_j slot, K-major, swizzled)
+        ok = mbar_wait(BAR(kDpFull), dp_cnt & 1, wctx, 421);
+        if (!ok) break;
+        ++dp_cnt;
+        tc_fence_after();
+        uint32_t dp[64];
+        tmem_ld32(tdP + lane_base + grp * 64, dp);
+        tmem_ld32(tdP + lane_base + grp * 64 + 32, dp + 32);
+        tmem_wait_ld();
+        uint8_t* slab = sRing + ((base + 2 * j + 1) % NS) * kTile + grp * kSlab;
+#pragma unroll
+        for (int ch = 0; ch < 8; ++ch) {
+          float d[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) d[e] = pr[ch * 8 + e] * (__uint_as_float(dp[ch * 8 + e]) - dlt);
+          uint4 v;
+          v.x = pack_bf16x2(d[0], d[1]);
+          v.y = pack_bf16x2(d[2], d[3]);
+          v.z = pack_bf16x2(d[4], d[5]);
+          v.w = pack_bf16x2(d[6], d[7]);
+          *reinterpret_cast<uint4*>(slab + row * 128 + ((ch ^ (row & 7)) << 4)) = v;
+        }
+        fence_proxy_async_smem();
+        tc_fence_before();
+        mbar_arrive(BAR(kDsFull));
+      }
+      if (!ok) break;
+      r_cnt += 2 * n;
+      // ---- epilogue: dQ * softmax_scale -> bf16 -> global
+      ok = mbar_wait(BAR(kDqFinal), fin_cnt & 1, wctx, 422);
+      if (!ok) break;
+      ++fin_cnt;
+      tc_fence_after();
+      uint32_t acc[64];
+      tmem_ld32(tdQ + lane_base + grp * 64, acc);
+      tmem_ld32(tdQ + lane_base + grp * 64 + 32, acc + 32);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(BAR(kDqFree));
+      if (seq < p.Sq) store_row_half(dq_row, acc, p.softmax_scale);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kBwdMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// 3. dK/dV kernel
+// ------------------------------------------------------------------------------------------------
+// smem: K | V | ring of 4 tiles (Q_i, dO_i alternating) | stats ring [4][2][128] f32 | barriers | misc
+constexpr int kDkvStages = 4;
+constexpr int kStatSlots = 4;
+constexpr int kDkvSmem = 2 * kTile + kDkvStages * kTile + kStatSlots * 1024 + BwdSmem::kBarBytes + BwdSmem::kMisc;
+
+__global__ void __launch_bounds__(kBwdThreads, 1)
+bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+               const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const BwdParams p) {
+  constexpr int NS = kDkvStages;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* sK = smem_raw;
+  uint8_t* sV = sK + kTile;
+  uint8_t* sRing = sV + kTile;
+  float* sStats = reinterpret_cast<float*>(sRing + NS * kTile);  // [slot][0: lse_log2, 1: delta][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sStats) + kStatSlots * 1024);
+  uint32_t& s_tmem_base = *reinterpret_cast<uint32_t*>(bars + 32);
+  volatile int& s_abort = *reinterpret_cast<volatile int*>(bars + 33);
+  if ((smem_u32(smem_raw) & 1023u) != 0) {
+    if (threadIdx.x == 0 && atomicCAS(p.status, 0, (int)kStatusBadIndex) == 0) p.status[2] = 997;
+    return;
+  }
+  const uint32_t bar_base = smem_u32(bars);
+  auto BAR = [&](int i) { return bar_base + (uint32_t)i * 8u; };
+  // kv_full, kv_empty, ring_full[NS], ring_empty[NS], s_full, dp_full, p_full, ds_full, fin, free
+  constexpr int kKvFull = 0, kKvEmpty = 1, kRFull = 2, kREmpty = 2 + NS, kSFull = 2 + 2 * NS, kDpFull = kSFull + 1,
+                kPFull = kDpFull + 1, kDsFull = kPFull + 1, kFinal = kDsFull + 1, kFree = kFinal + 1,
+                kNumBars = kFree + 1;
+  static_assert(kNumBars <= 32, "barrier slots");
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  WaitCtx wctx{&s_abort, p.status};
+  if (threadIdx.x == 0) {
+    s_abort = 0;
+    mbar_init(BAR(kKvFull), 1);
+    mbar_init(BAR(kKvEmpty), 1);
+    for (int i = 0; i < NS; ++i) {
+      mbar_init(BAR(kRFull + i), 1);
+      mbar_init(BAR(kREmpty + i), 1);
+    }
+    mbar_init(BAR(kSFull), 1);
+    mbar_init(BAR(kDpFull), 1);
+    mbar_init(BAR(kPFull), 256);
+    mbar_init(BAR(kDsFull), 256);
+    mbar_init(BAR(kFinal), 1);
+    mbar_init(BAR(kFree), 256);
+    mbar_fence_init();
+    fence_proxy_async_smem();
+  }
+  if (warp == kBwdMmaWarp) {
+    tmem_alloc(smem_u32(&s_tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = s_tmem_base;
+  const uint32_t tS = tmem, tdP = tmem + 128u, tdV = tmem + 256u, tdK = tmem + 384u;
+  const int num_work = p.B * p.H * p.Nkv;
+
+  // number of query tiles attending kv block nb of (b,h): the CSR rows of all query groups
+  auto total_rows = [&](int bh, int nb) {
+    int t = 0;
+    for (int g = 0; g < p.G; ++g) {
+      const int32_t* off = p.csr_offsets + ((long long)bh * p.G + g) * (p.Nkv + 1);
+      t += off[nb + 1] - off[nb];
+    }
+    return t;
+  };
+
+  if (warp == kBwdLoadWarp) {
+    uint32_t r_cnt = 0, kv_cnt = 0, tile_cnt = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+      const int nb = w % p.Nkv;
+      const int bh = w / p.Nkv;
+      const int h = bh % p.H, b = bh / p.H;
+      if (total_rows(bh, nb) == 0) continue;
+      ok = mbar_wait(BAR(kKvEmpty), (kv_cnt & 1) ^ 1, wctx, 500);
+      if (!ok) break;
+      ++kv_cnt;
+      if (lane == 0) {
+        mbar_arrive_expect_tx(BAR(kKvFull), 2 * kTile);
+        for (int sl = 0; sl < 2; ++sl) {
+          tma_load_4d(smem_u32(sK + sl * kSlab), &tm_k, BAR(kKvFull), sl * 64, nb * 128, h, b);
+          tma_load_4d(smem_u32(sV + sl * kSlab), &tm_v, BAR(kKvFull), sl * 64, nb * 128, h, b);
+        }
+      }
+      for (int g = 0; g < p.G && ok; ++g) {
+        const int32_t* off = p.csr_offsets + ((long long)bh * p.G + g) * (p.Nkv + 1);
+        const int beg = off[nb], end = off[nb + 1];
+        for (int e = beg; e < end && ok; ++e) {
+          const int qi = p.csr_indices[(long long)bh * p.idx_cap + e];
+          for (int which = 0; which < 2 && ok; ++which) {
+            const uint32_t stage = r_cnt % NS, ph = (r_cnt / NS) & 1;
+            ok = mbar_wait(BAR(kREmpty + stage), ph ^ 1, wctx, 501);
+            if (!ok) break;
+            if (lane == 0) {
+              const CUtensorMap* tm = which ? &tm_do : &tm_q;
+              mbar_arrive_expect_tx(BAR(kRFull + stage), kTile + (which ? 0 : 1024));
+              for (int sl = 0; sl < 2; ++sl)
+                tma_load_4d(smem_u32(sRing + stage * kTile + sl * kSlab), tm, BAR(kRFull + stage), sl * 64, qi * 128,
+                            h, b);
+              if (!which) {
+                // row statistics of this query tile travel with its Q tile
+                float* st = sStats + (tile_cnt % kStatSlots) * 256;
+                const long long srow = (long long)bh * ((long long)p.Nq * 128) + (long long)qi * 128;
+                bulk_load_1d(smem_u32(st), p.lse_log2 + srow, 512, BAR(kRFull + stage));
+                bulk_load_1d(smem_u32(st + 128), p.delta + srow, 512, BAR(kRFull + stage));
+              }
+            }
+            ++r_cnt;
+          }
+          ++tile_cnt;
+        }
+      }
+    }
+  } else if (warp == kBwdMmaWarp) {
+    uint32_t r_cnt = 0, kv_cnt = 0, p_cnt = 0, ds_cnt = 0, free_cnt = 0;
+    bool ok = true, first_item = true;
+    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+      const int nb = w % p.Nkv;
+      const int bh = w / p.Nkv;
+      const int T = total_rows(bh, nb);
+      if (T == 0) continue;
+      ok = mbar_wait(BAR(kKvFull), kv_cnt & 1, wctx, 510);
+      if (!ok) break;
+      ++kv_cnt;
+      const uint32_t base = r_cnt;  // Q_i at base+2i, dO_i at base+2i+1
+      auto stage_of = [&](uint32_t pos) { return pos % NS; };
+      auto wait_full = [&](uint32_t pos) {
+        return mbar_wait(BAR(kRFull + stage_of(pos)), (pos / NS) & 1, wctx, 511);
+      };
+      auto issue_s = [&](int i) -> bool {  // S^T = K Q_i^T
+        if (!wait_full(base + 2 * i)) return false;
+        tc_fence_after();
+        if (lane == 0) {
+          mma_ss_kk(tS, smem_u32(sK), smem_u32(sRing + stage_of(base + 2 * i) * kTile), false);
+          umma_commit(BAR(kSFull));
+        }
+        __syncwarp();
+        return true;
+      };
+      auto issue_dp = [&](int i) -> bool {  // dP^T = V dO_i^T
+        if (!wait_full(base + 2 * i + 1)) return false;
+        tc_fence_after();
+        if (lane == 0) {
+          mma_ss_kk(tdP, smem_u32(sV), smem_u32(sRing + stage_of(base + 2 * i + 1) * kTile), false);
+          umma_commit(BAR(kDpFull));
+        }
+        __syncwarp();
+        return true;
+      };
+      ok = issue_s(0);
+      if (ok) ok = issue_dp(0);
+      for (int i = 0; i < T && ok; ++i) {
+        ok = mbar_wait(BAR(kPFull), p_cnt & 1, wctx, 512);  // P^T_i in tensor memory
+        if (!ok) break;
+        ++p_cnt;
+        if (i == 0 && !first_item) {  // previous item's epilogue has drained dV / dK
+          ok = mbar_wait(BAR(kFree), free_cnt & 1, wctx, 513);
+          if (!ok) break;
+          ++free_cnt;
+        }
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sd = stage_of(base + 2 * i + 1);
+          mma_ts_kmn(tdV, tS, tS + 64u, smem_u32(sRing + sd * kTile), i > 0);  // dV += P^T dO_i
+          umma_commit(BAR(kREmpty + sd));
+        }
+        __syncwarp();
+        if (i + 1 < T) {
+          ok = issue_s(i + 1);
+          if (!ok) break;
+        }
+        ok = mbar_wait(BAR(kDsFull), ds_cnt & 1, wctx, 514);  // dS^T_i in tensor memory
+        if (!ok) break;
+        ++ds_cnt;
+        tc_fence_after();
+        if (lane == 0) {
+          const uint32_t sq = stage_of(base + 2 * i);
+          mma_ts_kmn(tdK, tdP, tdP + 64u, smem_u32(sRing + sq * kTile), i > 0);  // dK += dS^T Q_i
+          umma_commit(BAR(kREmpty + sq));
+        }
+        __syncwarp();
+        if (i + 1 < T) ok = issue_dp(i + 1);
+      }
+      if (!ok) break;
+      if (lane == 0) {
+        umma_commit(BAR(kFinal));
+        umma_commit(BAR(kKvEmpty));
+      }
+      __syncwarp();
+      r_cnt += 2 * T;
+      first_item = false;
+    }
+  } else if (warp < 8) {
+    const int grp = warp >> 2;
+    const int row = threadIdx.x & 127;  // kv token inside the block = tensor-memory lane
+    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    uint32_t s_cnt = 0, dp_cnt = 0, fin_cnt = 0, tile_cnt = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+      const int nb = w % p.Nkv;
+      const int bh = w / p.Nkv;
+      const int h = bh % p.H, b = bh / p.H;
+      const int T = total_rows(bh, nb);
+      const int kv = nb * 128 + row;
+      const bool kv_valid = kv < p.Sk;
+      __nv_bfloat16* dk_row = p.dk + b * p.dk_stride[0] + h * p.dk_stride[1] + (long long)kv * p.dk_stride[2] + grp * 64;
+      __nv_bfloat16* dv_row = p.dv + b * p.dv_stride[0] + h * p.dv_stride[1] + (long long)kv * p.dv_stride[2] + grp * 64;
+      if (T == 0) {
+        if (kv_valid) {
+#pragma unroll
+          for (int ch = 0; ch < 8; ++ch) {
+            reinterpret_cast<uint4*>(dk_row)[ch] = make_uint4(0, 0, 0, 0);
+            reinterpret_cast<uint4*>(dv_row)[ch] = make_uint4(0, 0, 0, 0);
+          }
+        }
+        continue;
+      }
+      for (int i = 0; i < T && ok; ++i) {
+        const float4* st_l = reinterpret_cast<const float4*>(sStats + (tile_cnt % kStatSlots) * 256 + grp * 64);
+        const float4* st_d = reinterpret_cast<const float4*>(sStats + (tile_cnt % kStatSlots) * 256 + 128 + grp * 64);
+        ++tile_cnt;
+        // ---- phase 1: P^T = exp2(S^T*scale - lse[q]) -> bf16 -> tensor memory (head of this group's S half)
+        ok = mbar_wait(BAR(kSFull), s_cnt & 1, wctx, 520);
+        if (!ok) break;
+        ++s_cnt;
+        tc_fence_after();
+        float pr[64];
+        {
+          uint32_t* u = reinterpret_cast<uint32_t*>(pr);
+          tmem_ld32(tS + lane_base + grp * 64, u);
+          tmem_ld32(tS + lane_base + grp * 64 + 32, u + 32);
+          tmem_wait_ld();
+        }
+#pragma unroll
+        for (int c4 = 0; c4 < 16; ++c4) {
+          const float4 l = st_l[c4];
+          pr[c4 * 4 + 0] = ex2_approx(fmaf(pr[c4 * 4 + 0], p.scale_log2, -l.x));
+          pr[c4 * 4 + 1] = ex2_approx(fmaf(pr[c4 * 4 + 1], p.scale_log2, -l.y));
+          pr[c4 * 4 + 2] = ex2_approx(fmaf(pr[c4 * 4 + 2], p.scale_log2, -l.z));
+          pr[c4 * 4 + 3] = ex2_approx(fmaf(pr[c4 * 4 + 3], p.scale_log2, -l.w));
+        }
+        if (!kv_valid) {
+#pragma unroll
+          for (int c = 0; c < 64; ++c) pr[c] = 0.f;
+        }
+        {
+          uint32_t pk[32];
+#pragma unroll
+          for (int e = 0; e < 32; ++e) pk[e] = pack_bf16x2(pr[2 * e], pr[2 * e + 1]);
+          tmem_st32(tS + lane_base + grp * 64, pk);
+          tmem_wait_st();
+        }
+        tc_fence_before();
+        mbar_arrive(BAR(kPFull));
+        // ---- phase 2: dS^T = P^T o (dP^T - delta[q]) -> bf16 -> tensor memory
+        ok = mbar_wait(BAR(kDpFull), dp_cnt & 1, wctx, 521);
+        if (!ok) break;
+        ++dp_cnt;
+        tc_fence_after();
+        uint32_t dp[64];
+        tmem_ld32(tdP + lane_base + grp * 64, dp);
+        tmem_ld32(tdP + lane_base + grp * 64 + 32, dp + 32);
+        tmem_wait_ld();
+        {
+          uint32_t pk[32];
+#pragma unroll
+          for (int c4 = 0; c4 < 16; ++c4) {
+            const float4 d = st_d[c4];
+            const float d0 = pr[c4 * 4 + 0] * (__uint_as_float(dp[c4 * 4 + 0]) - d.x);
+            const float d1 = pr[c4 * 4 + 1] * (__uint_as_float(dp[c4 * 4 + 1]) - d.y);
+            const float d2 = pr[c4 * 4 + 2] * (__uint_as_float(dp[c4 * 4 + 2]) - d.z);
+            const float d3 = pr[c4 * 4 + 3] * (__uint_as_float(dp[c4 * 4 + 3]) - d.w);
+            pk[c4 * 2] = pack_bf16x2(d0, d1);
+            pk[c4 * 2 + 1] = pack_bf16x2(d2, d3);
+          }
+          tmem_st32(tdP + lane_base + grp * 64, pk);
+          tmem_wait_st();
+        }
+        tc_fence_before();
+        mbar_arrive(BAR(kDsFull));
+      }
+      if (!ok) break;
+      // ---- epilogue
+      ok = mbar_wait(BAR(kFinal), fin_cnt & 1, wctx, 522);
+      if (!ok) break;
+      ++fin_cnt;
+      tc_fence_after();
+      uint32_t acc[64];
+      tmem_ld32(tdV + lane_base + grp * 64, acc);
+      tmem_ld32(tdV + lane_base + grp * 64 + 32, acc + 32);
+      tmem_wait_ld();
+      if (kv_valid) store_row_half(dv_row, acc, 1.0f);
+      tmem_ld32(tdK + lane_base + grp * 64, acc);
+      tmem_ld32(tdK + lane_base + grp * 64 + 32, acc + 32);
+      tmem_wait_ld();
+      tc_fence_before();
+      mbar_arrive(BAR(kFree));
+      if (kv_valid) store_row_half(dk_row, acc, p.softmax_scale);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kBwdMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+}  // namespace bsa
+
+using namespace bsa;
+
+extern "C" int64_t bsa_bwd_workspace_bytes(int32_t B, int32_t H, int32_t Sq, int32_t Sk, int32_t D) {
+  (void)Sk;
+  (void)D;
+  if (B < 1 || H < 1 || Sq < 1) return 0;
+  const int64_t nq = (Sq + 127) / 128;
+  return 2 * (int64_t)B * H * nq * 128 * (int64_t)sizeof(float);
+}
+
+extern "C" int bsa_bwd(const bsa_bwd_args* a, void* cuda_stream) {
+  if (!a) return set_error(BSA_ERR_INVALID, "bsa_bwd: null args");
+  if (a->blk != 128) return set_error(BSA_ERR_UNSUPPORTED, "bsa_bwd: only 128-token blocks are built");
+  if (a->D != 128) return set_error(BSA_ERR_UNSUPPORTED, "bsa_bwd: head dimension %d not built (128 only)", a->D);
+  if (a->B < 1 || a->H < 1 || a->Sq < 1 || a->Sk < 1) return set_error(BSA_ERR_INVALID, "bsa_bwd: non-positive extent");
+  if (!a->dout || !a->q || !a->k || !a->v || !a->out || !a->lse || !a->dq || !a->dk || !a->dv || !a->q2k_index ||
+      !a->csr_offsets || !a->csr_indices || !a->workspace || !a->status)
+    return set_error(BSA_ERR_INVALID, "bsa_bwd: null pointer");
+  if (a->num_q_groups < 1 || a->cap < 0) return set_error(BSA_ERR_INVALID, "bsa_bwd: bad metadata extents");
+  const int64_t need = bsa_bwd_workspace_bytes(a->B, a->H, a->Sq, a->Sk, a->D);
+  if (a->workspace_bytes < need) return set_error(BSA_ERR_WORKSPACE, "bsa_bwd: workspace of %lld bytes needed", (long long)need);
+  for (int i = 0; i < 3; ++i) {
+    if ((a->dq_stride[i] | a->dk_stride[i] | a->dv_stride[i] | a->o_stride[i] | a->do_stride[i]) % 8 != 0)
+      return set_error(BSA_ERR_INVALID, "bsa_bwd: strides must be multiples of 8 elements");
+  }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const int num_sms = bsa_num_sms(dev);
+  if (num_sms <= 0) return set_error(BSA_ERR_CUDA, "bsa_bwd: cannot query the SM count");
+
+  const int Nq = (a->Sq + 127) / 128, Nkv = (a->Sk + 127) / 128;
+  const long long rows_pad = (long long)a->B * a->H * Nq * 128;
+  float* lse_log2 = reinterpret_cast<float*>(a->workspace);
+  float* delta = lse_log2 + rows_pad;
+  bwd_preprocess_kernel<<<(unsigned)((rows_pad + 7) / 8), 256, 0, st>>>(
+      reinterpret_cast<const __nv_bfloat16*>(a->out), reinterpret_cast<const __nv_bfloat16*>(a->dout), a->lse, lse_log2,
+      delta, a->o_stride[0], a->o_stride[1], a->o_stride[2], a->do_stride[0], a->do_stride[1], a->do_stride[2], a->H,
+      a->Sq, Nq * 128, rows_pad);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "bwd preprocess launch: %s", cudaGetErrorString(e));
+
+  CUtensorMap tq, tdo, tk, tv;
+  {
+    uint64_t qd[4] = {128, (uint64_t)a->Sq, (uint64_t)a->H, (uint64_t)a->B};
+    uint64_t kd[4] = {128, (uint64_t)a->Sk, (uint64_t)a->H, (uint64_t)a->B};
+    uint32_t box[4] = {64, 128, 1, 1};
+    auto strides = [](const int64_t* s, uint64_t* out) {
+      out[0] = (uint64_t)s[2] * 2;
+      out[1] = (uint64_t)s[1] * 2;
+      out[2] = (uint64_t)s[0] * 2;
+    };
+    uint64_t sb[3];
+    int rc;
+    strides(a->q_stride, sb);
+    if ((rc = make_tensor_map(&tq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, a->q, qd, sb, box, "q"))) return rc;
+    strides(a->do_stride, sb);
+    if ((rc = make_tensor_map(&tdo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, a->dout, qd, sb, box, "dout"))) return rc;
+    strides(a->k_stride, sb);
+    if ((rc = make_tensor_map(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, a->k, kd, sb, box, "k"))) return rc;
+    strides(a->v_stride, sb);
+    if ((rc = make_tensor_map(&tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, a->v, kd, sb, box, "v"))) return rc;
+  }
+  BwdParams p{};
+  p.q2k_index = a->q2k_index;
+  p.q2k_nums = a->q2k_nums;
+  p.csr_offsets = a->csr_offsets;
+  p.csr_indices = a->csr_indices;
+  p.lse_log2 = lse_log2;
+  p.delta = delta;
+  p.dq = reinterpret_cast<__nv_bfloat16*>(a->dq);
+  p.dk = reinterpret_cast<__nv_bfloat16*>(a->dk);
+  p.dv = reinterpret_cast<__nv_bfloat16*>(a->dv);
+  p.status = a->status;
+  for (int i = 0; i < 3; ++i) {
+    p.dq_stride[i] = a->dq_stride[i];
+    p.dk_stride[i] = a->dk_stride[i];
+    p.dv_stride[i] = a->dv_stride[i];
+  }
+  const long long idx_cap = (long long)Nq * a->cap > 1 ? (long long)Nq * a->cap : 1;
+  p.idx_cap = idx_cap;
+  p.fixed_count = a->block_sparse_num;
+  p.cap = a->cap;
+  p.B = a->B;
+  p.H = a->H;
+  p.Sq = a->Sq;
+  p.Sk = a->Sk;
+  p.Nq = Nq;
+  p.Nkv = Nkv;
+  p.G = a->num_q_groups;
+  p.softmax_scale = a->softmax_scale;
+  p.scale_log2 = a->softmax_scale * kLog2e;
+
+  e = cudaFuncSetAttribute(bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmem);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDkvSmem);
+  if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "bsa_bwd: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  const long long work_q = (long long)a->B * a->H * Nq, work_kv = (long long)a->B * a->H * Nkv;
+  if (work_q > 0x7fffffffLL || work_kv > 0x7fffffffLL) return set_error(BSA_ERR_UNSUPPORTED, "bsa_bwd: too many tiles");
+  const int grid_q = (int)(work_q < num_sms ? work_q : num_sms);
+  const int grid_kv = (int)(work_kv < num_sms ? work_kv : num_sms);
+  bwd_dq_kernel<<<grid_q, kBwdThreads, kDqSmem, st>>>(tq, tdo, tk, tv, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "bwd dQ launch: %s", cudaGetErrorString(e));
+  bwd_dkv_kernel<<<grid_kv, kBwdThreads, kDkvSmem, st>>>(tq, tdo, tk, tv, p);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "bwd dK/dV launch: %s", cudaGetErrorString(e));
+  return BSA_OK;
+}

@@ -81,27 +81,46 @@ struct WaitCtx {
 };
 
 // Returns true when the phase with the given parity has completed, false when the CTA is aborting.
+// Must be called by all 32 lanes of a warp: the answer is made warp-uniform, so that warp-collective
+// instructions that follow are never executed by a partial warp.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
                                           int site) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint64_t t0 = globaltimer_ns();
-  uint32_t it = 0;
-  for (;;) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((++it & 0xffu) == 0) {
-      if (*ctx.abort_flag) return false;
-      if (globaltimer_ns() - t0 > BSA_WAIT_LIMIT_NS) {
-        *ctx.abort_flag = 1;
-        if (atomicCAS(ctx.status, 0, (int)kStatusWaitTimeout) == 0) {
-          ctx.status[1] = (int)blockIdx.x;
-          ctx.status[2] = site;
-          ctx.status[3] = (int)threadIdx.x;
+  bool done = mbar_try_wait(bar, parity);
+  if (!done) {
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t it = 0;
+    for (;;) {
+      if (mbar_try_wait(bar, parity)) {
+        done = true;
+        break;
+      }
+      if ((++it & 0xffu) == 0) {
+        if (*ctx.abort_flag) break;
+        if (globaltimer_ns() - t0 > BSA_WAIT_LIMIT_NS) {
+          *ctx.abort_flag = 1;
+          if (atomicCAS(ctx.status, 0, (int)kStatusWaitTimeout) == 0) {
+            ctx.status[1] = (int)blockIdx.x;
+            ctx.status[2] = site;
+            ctx.status[3] = (int)threadIdx.x;
+          }
+          __threadfence();
+          break;
         }
-        __threadfence();
-        return false;
       }
     }
   }
+  return __all_sync(0xffffffffu, done);
+}
+
+// Rendezvous of `count` threads through an mbarrier initialised with that count: arrive, then a
+// bounded wait.  Unlike bar.sync it cannot strand the threads that are already waiting when another
+// role aborts.  `phase_cnt` counts the uses of this barrier by the calling thread.
+__device__ __forceinline__ bool mbar_rendezvous(uint32_t bar, uint32_t& phase_cnt, const WaitCtx& ctx,
+                                                int site) {
+  mbar_arrive(bar);
+  const bool ok = mbar_wait(bar, phase_cnt & 1, ctx, site);
+  ++phase_cnt;
+  return ok;
 }
 
 // ---------------------------------------------------------------------------------------------

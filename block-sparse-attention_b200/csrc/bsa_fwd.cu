@@ -50,9 +50,6 @@ constexpr int kSoftmaxThreads = 256;
 constexpr int kMmaWarp = 8;
 constexpr int kLoadWarp = 9;
 
-// barrier ids for named barriers (0 is __syncthreads)
-constexpr int kBarSoftmaxAll = 1;
-constexpr int kBarGroup0 = 2;  // +group
 
 template <bool FP8>
 struct FwdCfg {
@@ -65,8 +62,8 @@ struct FwdCfg {
   static constexpr int kMmaK = FP8 ? 32 : 16;
   static constexpr int kKSteps = 128 / kMmaK;
   static constexpr int kPColsPerStep = FP8 ? 8 : 8;  // tensor-memory columns of P per MMA k step
-  // smem: Q | O | KV stages | barriers
-  static constexpr int kSmemBytes = kTileBytes + kOBytes + kStages * kTileBytes + 1024 /*align*/ + 512;
+  // smem: Q | O | KV stages | 32 barriers | stats [2][128] float2 | tmem base, abort flag
+  static constexpr int kSmemBytes = kTileBytes + kOBytes + kStages * kTileBytes + 256 + 2048 + 16;
 };
 
 struct WorkItem {
@@ -123,11 +120,10 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                const FwdParams p) {
   using Cfg = FwdCfg<FP8>;
   constexpr int NS = Cfg::kStages;
-  constexpr int kPerIt = 128 / BLK;
-
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~(uintptr_t)1023);
+  // everything lives in dynamic shared memory (no static allocation), so the 1024-byte alignment the
+  // swizzled tiles need comes from the declaration itself and no slack has to be reserved
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
   uint8_t* sQ = smem;
   uint8_t* sO = sQ + Cfg::kTileBytes;
   uint8_t* sKV = sO + Cfg::kOBytes;
@@ -138,10 +134,15 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const uint32_t bar_base = smem_u32(bars);
   auto BAR = [&](int i) { return bar_base + (uint32_t)i * 8u; };
   constexpr int kQFull = 0, kQEmpty = 1, kKvFull = 2, kKvEmpty = 2 + NS, kSFull = 2 + 2 * NS,
-                kPFull = kSFull + 2, kOFinal = kPFull + 2, kNumBars = kOFinal + 1;
-  __shared__ uint32_t s_tmem_base;
-  __shared__ int s_abort;
-  __shared__ float2 s_stats[2][128];
+                kPFull = kSFull + 2, kOFinal = kPFull + 2, kEpiA = kOFinal + 1, kEpiB = kEpiA + 1,
+                kGrpA = kEpiB + 1, kGrpB = kGrpA + 2, kNumBars = kGrpB + 2;
+  float2 (*s_stats)[128] = reinterpret_cast<float2 (*)[128]>(bars + 32);  // [2][128] (max, sum)
+  uint32_t& s_tmem_base = *reinterpret_cast<uint32_t*>(bars + 32 + 256);
+  volatile int& s_abort = *reinterpret_cast<volatile int*>(bars + 32 + 256 + 1);
+  if ((smem_u32(smem_raw) & 1023u) != 0) {  // uniform over the CTA: nothing has been set up yet
+    if (threadIdx.x == 0 && atomicCAS(p.status, 0, (int)kStatusBadIndex) == 0) p.status[2] = 999;
+    return;
+  }
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -160,6 +161,12 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       mbar_init(BAR(kPFull + s), 128);
     }
     mbar_init(BAR(kOFinal), 1);
+    mbar_init(BAR(kEpiA), kSoftmaxThreads);
+    mbar_init(BAR(kEpiB), kSoftmaxThreads);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(BAR(kGrpA + s), 128);
+      mbar_init(BAR(kGrpB + s), 128);
+    }
     mbar_fence_init();
     fence_proxy_async_smem();
   }
@@ -341,7 +348,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const int row = threadIdx.x & 127;         // query row inside the tile = tensor-memory lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const bool row_active = (BLK == 128) || (row < 64);  // warp-uniform
-    uint32_t s_cnt = 0, of_cnt = 0;
+    uint32_t s_cnt = 0, of_cnt = 0, epi_a = 0, epi_b = 0, grp_a = 0, grp_b = 0;
     bool ok = true;
     const bool need_mask_meta = (p.block_sizes != nullptr) || (p.Sk % BLK != 0);
     constexpr float kRescaleThreshold = FP8 ? 1.8073549f /* log2(448/128) */ : 8.0f;
@@ -531,7 +538,8 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         tc_fence_after();
       }
       s_stats[grp][row] = make_float2(m_cur, l_sum);
-      named_bar_sync(kBarSoftmaxAll, kSoftmaxThreads);
+      ok = mbar_rendezvous(BAR(kEpiA), epi_a, wctx, 320);
+      if (!ok) break;
       const float2 st0 = s_stats[0][row];
       const float2 st1 = s_stats[1][row];
       const float m_all = fmaxf(st0.x, st1.x);
@@ -566,7 +574,8 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
       tc_fence_before();
       // all reads of O0/O1 and of the stats are done: the next tile may overwrite them
-      named_bar_sync(kBarSoftmaxAll, kSoftmaxThreads);
+      ok = mbar_rendezvous(BAR(kEpiB), epi_b, wctx, 321);
+      if (!ok) break;
 
       if (FP8) {
         const float* vs = p.v_scale + (long long)hq * 128 + grp * 64;
@@ -588,7 +597,8 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         // stage bf16 in shared memory in the 128-byte-swizzled layout the output tensor map expects
         const bool issuer = (threadIdx.x & 127) == 0;
         if (issuer) tma_store_wait_read<0>();
-        named_bar_sync(kBarGroup0 + grp, 128);
+        ok = mbar_rendezvous(BAR(kGrpA + grp), grp_a, wctx, 322);
+        if (!ok) break;
         if (row_active) {
           uint8_t* slab = sO + grp * (128 * 128);
 #pragma unroll
@@ -602,7 +612,8 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
         }
         fence_proxy_async_smem();
-        named_bar_sync(kBarGroup0 + grp, 128);
+        ok = mbar_rendezvous(BAR(kGrpB + grp), grp_b, wctx, 323);
+        if (!ok) break;
         if (issuer) {
           const int cs = t.m * seq_per_tile;
           tma_store_5d(&tm_o, smem_u32(sO + grp * (128 * 128)), grp * 64, t.g, cs, t.hkv, t.b);
@@ -635,12 +646,10 @@ static int launch_fwd(const bsa_fwd_args& a, const FwdParams& p, const CUtensorM
                       int num_sms, cudaStream_t stream) {
   using Cfg = FwdCfg<FP8>;
   auto kern = bsa_fwd_kernel<BLK, FP8, SPLIT>;
-  static bool configured = false;
-  if (!configured) {
+  {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          Cfg::kSmemBytes);
     if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "cudaFuncSetAttribute(smem): %s", cudaGetErrorString(e));
-    configured = true;
   }
   const int grid = p.num_work < num_sms ? p.num_work : num_sms;
   if (grid <= 0) return BSA_OK;

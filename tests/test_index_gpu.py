@@ -1,0 +1,87 @@
+"""GPU parity (bit-exact) of the index kernels against the CPU oracle and the reference's CSR model."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import load_golden
+from oracle import bsa_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _assert_csr(q2k, bsn, nkv, bucket, nums):
+    from block_sparse_attention.bsa_attn_interface import _build_bucketed_k2q_csr
+    offsets, indices, G, rows_per_group = _build_bucketed_k2q_csr(
+        q2k.cuda(), bsn, nkv, bucket_size_blocks=bucket, q2k_block_nums=None if nums is None else nums.cuda())
+    exp_off, exp_rows = orc.bucketed_k2q_csr(q2k, bsn, nkv, bucket, nums)
+    assert offsets.dtype == torch.int32 and indices.dtype == torch.int32
+    assert G == exp_off.shape[2] and rows_per_group == nkv
+    assert indices.shape[-1] == max(1, q2k.shape[2] * q2k.shape[3])
+    assert torch.equal(offsets.cpu(), exp_off)
+    off, idx = offsets.cpu(), indices.cpu()
+    B, H = off.shape[:2]
+    for b in range(B):
+        for h in range(H):
+            for g in range(G):
+                for j in range(nkv):
+                    row = idx[b, h, off[b, h, g, j]:off[b, h, g, j + 1]].tolist()
+                    assert row == sorted(exp_rows[(b, h, g, j)]), (b, h, g, j)  # already ascending
+    return offsets, indices
+
+
+@pytest.mark.parametrize("name", ["csr_literal_variable.npz", "csr_random_fixed.npz", "csr_topk_1025.npz"])
+def test_csr_golden(name):
+    g = load_golden(name)
+    q2k = torch.from_numpy(g["q2k"])
+    nums = torch.from_numpy(g["nums"]) if g["nums"].size else None
+    offsets, _ = _assert_csr(q2k, int(g["bsn"]), int(g["nkv"]), int(g["bucket"]), nums)
+    assert np.array_equal(offsets.cpu().numpy(), g["offsets"])
+
+
+def test_csr_empty_edge_width():
+    """tests/test_bucketed_k2q_csr.py:225-243: zero-width index."""
+    q2k = torch.empty((1, 1, 2, 0), dtype=torch.int32)
+    nums = torch.zeros((1, 1, 2), dtype=torch.int32)
+    _assert_csr(q2k, 0, 3, 1, nums)
+
+
+def test_csr_config2_shape_deterministic():
+    gen = torch.Generator().manual_seed(0)
+    q2k = orc.make_uniform_index(1, 2, 256, 256, 26, gen)
+    o1, i1 = _assert_csr(q2k, 26, 256, 384, None)
+    o2, i2 = _assert_csr(q2k, 26, 256, 100, None)  # three query groups
+    from block_sparse_attention.bsa_attn_interface import _build_bucketed_k2q_csr
+    o3, i3, _, _ = _build_bucketed_k2q_csr(q2k.cuda(), 26, 256, bucket_size_blocks=384)
+    assert torch.equal(o1, o3) and torch.equal(i1[..., :256 * 26], i3[..., :256 * 26])
+
+
+def test_csr_long_rows_global_sort_path():
+    """every q block selects kv block 0: one CSR row of 1500 entries (> the shared-memory sort limit)."""
+    q2k = torch.zeros((1, 1, 1500, 2), dtype=torch.int32)
+    q2k[..., 1] = 1
+    _assert_csr(q2k, 2, 3, 2000, None)
+
+
+def test_q2k_to_k2q_set_semantics():
+    from block_sparse_attention import convert_q2k_to_k2q
+    gen = torch.Generator().manual_seed(2)
+    q2k = torch.randint(-1, 14, (2, 3, 9, 7), generator=gen, dtype=torch.int32)  # duplicates, -1 and 13 out of range
+    nums = torch.randint(-1, 9, (2, 3, 9), generator=gen, dtype=torch.int32)
+    for n in (None, nums):
+        k2q, k2q_nums = convert_q2k_to_k2q(q2k.cuda(), 5, 13, None if n is None else n.cuda())
+        e_k2q, e_nums = orc.q2k_to_k2q(q2k, 5, 13, n)
+        assert torch.equal(k2q.cpu(), e_k2q) and torch.equal(k2q_nums.cpu(), e_nums)
+
+
+def test_mask_to_q2k_roundtrip_and_clamp():
+    from block_sparse_attention import block_mask_to_q2k
+    gen = torch.Generator().manual_seed(4)
+    mask = torch.rand(2, 2, 37, 300, generator=gen) < 0.1
+    mask[0, 0, 0] = False
+    mask[1, 1, 5] = True
+    index, nums = block_mask_to_q2k(mask.cuda())
+    e_index, e_nums = orc.mask_to_q2k(mask)
+    assert torch.equal(index.cpu(), e_index) and torch.equal(nums.cpu(), e_nums)
+    index, nums = block_mask_to_q2k(mask.cuda(), max_kv_blocks=16)
+    e_index, e_nums = orc.mask_to_q2k(mask, 16)
+    assert torch.equal(index.cpu(), e_index) and torch.equal(nums.cpu(), e_nums)
