@@ -622,13 +622,15 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const int grp = warp >> 2;
     const int row = threadIdx.x & 127;  // kv token inside the block = tensor-memory lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    uint32_t s_cnt = 0, dp_cnt = 0, fin_cnt = 0, tile_cnt = 0;
+    uint32_t s_cnt = 0, dp_cnt = 0, fin_cnt = 0, tile_cnt = 0, r_cnt = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
       const int nb = w % p.Nkv;
       const int bh = w / p.Nkv;
       const int h = bh % p.H, b = bh / p.H;
       const int T = total_rows(bh, nb);
+      const uint32_t base = r_cnt;
+      r_cnt += 2 * T;
       const int kv = nb * 128 + row;
       const bool kv_valid = kv < p.Sk;
       __nv_bfloat16* dk_row = p.dk + b * p.dk_stride[0] + h * p.dk_stride[1] + (long long)kv * p.dk_stride[2] + grp * 64;
@@ -651,6 +653,13 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         ok = mbar_wait(BAR(kSFull), s_cnt & 1, wctx, 520);
         if (!ok) break;
         ++s_cnt;
+        {
+          // observe the arrival of this tile's row statistics directly (they were copied on the Q
+          // stage's barrier); the phase cannot have advanced further: the stage is held until dK
+          const uint32_t pos = base + 2 * (uint32_t)i;
+          ok = mbar_wait(BAR(kRFull + pos % NS), (pos / NS) & 1, wctx, 523);
+          if (!ok) break;
+        }
         tc_fence_after();
         float pr[64];
         {

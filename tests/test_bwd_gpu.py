@@ -1,0 +1,142 @@
+"""GPU parity of the backward pass (BF16, MHA, D = 128, 128-token blocks) against torch autograd on the
+CPU oracle.  Tolerance per gradient is the reference's: 3 * |bf16 autograd - fp32 autograd|max +
+3 * bf16 round-trip eps + 5e-3 (tests/test_flash_bwd.py:53-61)."""
+import math
+
+import pytest
+import torch
+
+from helpers import bf16_from_bits, bf16_roundtrip_eps, load_golden
+from oracle import bsa_oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+
+def _run(q, k, v, do, index, count, nums=None, scale=None, layout="bhsd", bucket=None, bufs=False):
+    from block_sparse_attention import bsa_attn_bwd, bsa_attn_fwd
+    c = lambda t: None if t is None else t.cuda()
+    qc, kc, vc, doc, ic, nc = c(q), c(k), c(v), c(do), c(index), c(nums)
+    if layout == "bshd":
+        qc, kc, vc, doc = (t.transpose(1, 2).contiguous() for t in (qc, kc, vc, doc))
+    out, lse = bsa_attn_fwd(qc, kc, vc, ic, count, q2k_block_nums=nc, softmax_scale=scale, return_lse=True,
+                            layout=layout, sparse_block_size=128)
+    kw = {}
+    if bufs:
+        kw = dict(dq=torch.full_like(qc, 7.0), dk=torch.full_like(kc, 7.0), dv=torch.full_like(vc, 7.0))
+    dq, dk, dv = bsa_attn_bwd(doc, qc, kc, vc, out, lse, ic, count, q2k_block_nums=nc, softmax_scale=scale,
+                              bucket_size_blocks=bucket, layout=layout, sparse_block_size=128, **kw)
+    if bufs:
+        assert dq is kw["dq"] and dk is kw["dk"] and dv is kw["dv"]
+    if layout == "bshd":
+        dq, dk, dv = (t.transpose(1, 2) for t in (dq, dk, dv))
+    return dq.float().cpu(), dk.float().cpu(), dv.float().cpu()
+
+
+def _check(got, q, k, v, do, bias, scale):
+    # Rows that attend nothing make the dense autograd reference NaN everywhere (softmax of an all -inf
+    # row).  Such rows contribute nothing to any gradient, so for the reference they are given one
+    # arbitrary column and a zero upstream gradient, which yields exactly that.
+    empty = torch.isinf(bias).all(dim=-1)
+    if empty.any():
+        bias = bias.clone()
+        do = do.clone()
+        bias[..., 0] = torch.where(empty, torch.zeros_like(bias[..., 0]), bias[..., 0])
+        do[empty] = 0
+    _, _, *ref = orc.backward_dense(q, k, v, do, bias, scale, upcast=True)
+    _, _, *pt = orc.backward_dense(q, k, v, do, bias, scale, upcast=False)
+    for name, g, r, p in zip(("dq", "dk", "dv"), got, ref, pt):
+        r = torch.nan_to_num(r.float(), nan=0.0, posinf=0.0, neginf=0.0)
+        p = torch.nan_to_num(p.float(), nan=0.0, posinf=0.0, neginf=0.0)
+        tol = 3 * (p - r).abs().max().item() + 3 * bf16_roundtrip_eps(r) + 5e-3
+        err = (g - r).abs().max().item()
+        assert torch.isfinite(g).all(), name
+        assert err <= tol, f"{name}: max err {err} > tol {tol}"
+
+
+def test_golden_backward():
+    g = load_golden("bwd_dense.npz")
+    q, k, v, do = (bf16_from_bits(g[n]) for n in ("q", "k", "v", "dout"))
+    index = torch.from_numpy(g["index"])
+    got = _run(q, k, v, do, index, 2)
+    for name, t in zip(("dq", "dk", "dv"), got):
+        ref = torch.from_numpy(g[name])
+        assert (t - ref).abs().max().item() < 3e-2, name
+    S = q.shape[2]
+    bias = orc.block_sparse_to_attn_bias(index, 2, torch.full((3,), 128, dtype=torch.int32), S, S)
+    _check(got, q, k, v, do, bias, 1 / math.sqrt(128))
+
+
+def _case(seed, B, H, Sq, Sk, counts, poison=True):
+    gen = torch.Generator().manual_seed(seed)
+    q, do = (torch.randn(B, H, Sq, 128, generator=gen).bfloat16() for _ in range(2))
+    k, v = (torch.randn(B, H, Sk, 128, generator=gen).bfloat16() for _ in range(2))
+    Nq, Nkv = math.ceil(Sq / 128), math.ceil(Sk / 128)
+    index = torch.zeros(B, H, Nq, Nkv, dtype=torch.int32)
+    nums = torch.zeros(B, H, Nq, dtype=torch.int32)
+    i = 0
+    for b in range(B):
+        for h in range(H):
+            for m in range(Nq):
+                n = min(counts[i % len(counts)], Nkv)
+                i += 1
+                nums[b, h, m] = n
+                index[b, h, m] = torch.randperm(Nkv, generator=gen).int()
+                if poison:
+                    index[b, h, m, n:] = 0x3FFFFFFF
+    return q, k, v, do, index, nums
+
+
+@pytest.mark.parametrize("Sq,Sk,counts", [(512, 512, [2, 4, 1, 3]), (1024, 1280, [0, 1, 2, 3, 4, 7, 8, 9]),
+                                          (300, 700, [3, 0, 6]), (128, 2048, [16])])
+def test_variable_counts_tails_and_empty_rows(Sq, Sk, counts):
+    q, k, v, do, index, nums = _case(1, 1, 2, Sq, Sk, counts)
+    got = _run(q, k, v, do, index, 0, nums=nums)
+    Nkv = math.ceil(Sk / 128)
+    sizes = torch.full((Nkv,), 128, dtype=torch.int32)
+    sizes[-1] = Sk - (Nkv - 1) * 128
+    clean = index.clamp(max=Nkv - 1)
+    bias = orc.block_sparse_to_attn_bias(clean, 0, sizes, Sq, Sk, q2k_block_nums=nums)
+    _check(got, q, k, v, do, bias, 1 / math.sqrt(128))
+    # kv blocks nobody attends and empty query tiles get exact zeros
+    attended = torch.zeros(Nkv, dtype=torch.bool)
+    for m in range(index.shape[2]):
+        attended[clean[0, 0, m, :int(nums[0, 0, m])].long()] = True
+    for j in range(Nkv):
+        if not attended[j]:
+            assert (got[1][0, 0, j * 128:(j + 1) * 128] == 0).all() and (got[2][0, 0, j * 128:(j + 1) * 128] == 0).all()
+
+
+def test_fixed_count_multi_bucket_bshd_and_buffers():
+    q, k, v, do, index, _ = _case(2, 2, 2, 768, 768, [4], poison=False)
+    bias = orc.block_sparse_to_attn_bias(index, 4, torch.full((6,), 128, dtype=torch.int32), 768, 768)
+    scale = 0.07
+    a = _run(q, k, v, do, index, 4, scale=scale, bucket=2)            # three query groups
+    b = _run(q, k, v, do, index, 4, scale=scale, bucket=None, layout="bshd", bufs=True)
+    _check(a, q, k, v, do, bias, scale)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y), "grouping / layout must not change the result"
+
+
+def test_repeat_calls_are_bit_identical_many_tiles():
+    """more work items than SMs in both kernels; deterministic accumulation order."""
+    q, k, v, do, index, nums = _case(3, 2, 4, 2048, 2048, [5, 3, 8, 1, 0, 6])
+    a = _run(q, k, v, do, index, 0, nums=nums)
+    b = _run(q, k, v, do, index, 0, nums=nums)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+    gq, gk, gv = orc.backward_gathered(q, k, v, do, index.clamp(max=15), 0, nums=nums, heads=[1], batches=[1])
+    for got, ref in zip(a, (gq, gk, gv)):
+        assert (got[1, 1] - ref[1, 1]).abs().max().item() < 6e-2
+
+
+def test_argument_errors():
+    from block_sparse_attention import bsa_attn_bwd
+    x = torch.zeros(1, 2, 128, 128, device="cuda").bfloat16()
+    lse = torch.zeros(1, 2, 128, device="cuda")
+    idx = torch.zeros(1, 2, 1, 1, dtype=torch.int32, device="cuda")
+    with pytest.raises(AssertionError):
+        bsa_attn_bwd(x, x, x, x, x, lse, idx, 1, sparse_block_size=32)
+    with pytest.raises(AssertionError):
+        bsa_attn_bwd(x.half(), x.half(), x.half(), x.half(), x.half(), lse, idx, 1, sparse_block_size=128)
+    with pytest.raises(AssertionError):
+        bsa_attn_bwd(x, x, x[:, :1], x[:, :1], x, lse, idx, 1, sparse_block_size=128)  # GQA
