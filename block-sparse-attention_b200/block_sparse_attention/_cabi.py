@@ -13,7 +13,8 @@ from typing import Dict, Optional
 import torch
 
 _HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(_HERE, "libbsa_b200.so")
+# BSA_B200_LIB points at another build of the same library (e.g. one compiled with development timers)
+LIB_PATH = os.environ.get("BSA_B200_LIB") or os.path.join(_HERE, "libbsa_b200.so")
 
 BSA_DTYPE_BF16 = 0
 BSA_DTYPE_E4M3 = 1

@@ -6,6 +6,8 @@
 //   warps 4-7  softmax group 1: owns stream 1 (KV iterations 1, 3, 5, ...)
 //   warp  8    MMA issue (one lane)
 //   warp  9    TMA producer (one lane)
+//   warps 10-11 idle: they complete the third warpgroup so that registers can be re-partitioned
+//              (setmaxnreg) in favour of the softmax groups
 // Tensor memory (512 columns): S0 @0, S1 @128, O0 @256, O1 @384 (fp32, 128 lanes x 128 columns each);
 // the probabilities P_s overwrite the head of S_s (bf16: 64 columns, e4m3: 32 columns) and are the
 // A operand of the PV MMA straight from tensor memory.  The two streams keep independent running
@@ -22,6 +24,21 @@
 #include "../../include/bsa_b200.h"
 #include "bsa_common.cuh"
 #include "bsa_host.h"
+
+// Optional per-role phase timers (development aid, compiled out unless BSA_PHASE_TIMERS is defined):
+// lane 0 of one warp per role accumulates clock64() deltas and adds them to a caller buffer of 64 u64
+// passed in the otherwise unused partial_lse pointer of an unsplit launch.
+#ifdef BSA_PHASE_TIMERS
+#define PT_DECL unsigned long long pt_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; unsigned long long pt_t = clock64();
+#define PT_MARK(i) { const unsigned long long pt_n = clock64(); pt_acc[i] += pt_n - pt_t; pt_t = pt_n; }
+#define PT_FLUSH(base) if (lane == 0 && p.partial_lse != nullptr) { \
+    unsigned long long* pt_g = reinterpret_cast<unsigned long long*>(p.partial_lse); \
+    for (int pt_i = 0; pt_i < 8; ++pt_i) atomicAdd(pt_g + (base) + pt_i, pt_acc[pt_i]); }
+#else
+#define PT_DECL
+#define PT_MARK(i)
+#define PT_FLUSH(base)
+#endif
 
 namespace bsa {
 
@@ -45,7 +62,7 @@ struct FwdParams {
   float scale_log2;
 };
 
-constexpr int kThreads = 320;
+constexpr int kThreads = 384;  // warps 10-11 only give their registers away
 constexpr int kSoftmaxThreads = 256;
 constexpr int kMmaWarp = 8;
 constexpr int kLoadWarp = 9;
@@ -192,16 +209,20 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
   if (warp == kLoadWarp) {
     // ======================================= TMA producer =======================================
+    setmaxnreg_dec<56>();
     uint32_t kv_cnt = 0;  // stages produced so far
     uint32_t q_cnt = 0;
     bool ok = true;
+    PT_DECL
     for (int w = blockIdx.x; w < p.num_work && ok; w += gridDim.x) {
       const WorkItem t = decode_work<BLK>(p, w);
       const int n_it = t.it_end - t.it_begin;
       if (n_it <= 0) continue;
+      PT_MARK(0)
       // Q tile
       ok = mbar_wait(BAR(kQEmpty), (q_cnt & 1) ^ 1, wctx, 100);
       if (!ok) break;
+      PT_MARK(1)
       if (lane == 0) {
         // a 64-row query tile fills only the top half of each slab
         mbar_arrive_expect_tx(BAR(kQFull), Cfg::kSlabs * BLK * 128);
@@ -217,7 +238,9 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       auto issue_tile = [&](const CUtensorMap* tm, int blk0, int blk1) -> bool {
         const uint32_t stage = kv_cnt % NS;
         const uint32_t ph = (kv_cnt / NS) & 1;
+        PT_MARK(0)
         if (!mbar_wait(BAR(kKvEmpty + stage), ph ^ 1, wctx, 101)) return false;
+        PT_MARK(2)
         if (lane == 0) {
           uint8_t* dst = sKV + stage * Cfg::kTileBytes;
           mbar_arrive_expect_tx(BAR(kKvFull + stage), Cfg::kTileBytes);
@@ -262,41 +285,48 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         pj1 = j1;
       }
     }
+    PT_FLUSH(48)
   } else if (warp == kMmaWarp) {
     // ========================================= MMA issue ========================================
+    setmaxnreg_dec<56>();
     constexpr uint32_t kFmt = FP8 ? 0u : 1u;  // e4m3 / bf16
     constexpr uint32_t idesc_qk = umma_idesc(kFmt, kFmt, 0, 0, 128, 128);
     constexpr uint32_t idesc_pv = umma_idesc(kFmt, kFmt, 0, 1, 128, 128);
     uint32_t kv_cnt = 0, q_cnt = 0;
     uint32_t p_cnt[2] = {0, 0};
     bool ok = true;
+    // descriptors are built once; a byte offset b inside a tile is an addition of b >> 4 to the low word
+    const uint64_t q_desc = umma_desc_sw128(smem_u32(sQ), 0, 1024);
+    const uint64_t k_desc0 = umma_desc_sw128(smem_u32(sKV), 0, 1024);                               // K-major view
+    const uint64_t v_desc0 = umma_desc_sw128(smem_u32(sKV), FP8 ? 0u : (uint32_t)Cfg::kSlabBytes, 1024);  // MN-major
+    PT_DECL
     for (int w = blockIdx.x; w < p.num_work && ok; w += gridDim.x) {
       const WorkItem t = decode_work<BLK>(p, w);
       const int n_it = t.it_end - t.it_begin;
       if (n_it <= 0) continue;
+      PT_MARK(0)
       ok = mbar_wait(BAR(kQFull), q_cnt & 1, wctx, 200);
       if (!ok) break;
+      PT_MARK(1)
       ++q_cnt;
       tc_fence_after();
 
       auto issue_qk = [&](int i) -> bool {
         const uint32_t stage = kv_cnt % NS;
         const uint32_t ph = (kv_cnt / NS) & 1;
+        PT_MARK(0)
         if (!mbar_wait(BAR(kKvFull + stage), ph, wctx, 201)) return false;
+        PT_MARK(2)
         tc_fence_after();
         if (lane == 0) {
-          const uint32_t a0 = smem_u32(sQ);
-          const uint32_t b0 = smem_u32(sKV + stage * Cfg::kTileBytes);
+          const uint64_t kd = k_desc0 + (uint64_t)stage * (Cfg::kTileBytes >> 4);
 #pragma unroll
           for (int k = 0; k < Cfg::kKSteps; ++k) {
             // 32 bytes of K extent per step inside a 128-byte swizzled row; bf16 tiles continue in
             // the second slab after four steps.
-            const uint32_t off = FP8 ? (uint32_t)k * 32u
-                                     : (uint32_t)(k >> 2) * Cfg::kSlabBytes + (uint32_t)(k & 3) * 32u;
-            const uint64_t da = umma_desc_sw128(a0 + off, 0, 1024);
-            const uint64_t db = umma_desc_sw128(b0 + off, 0, 1024);
-            if (FP8) umma_f8_ss(tS[i & 1], da, db, idesc_qk, k > 0);
-            else umma_f16_ss(tS[i & 1], da, db, idesc_qk, k > 0);
+            const uint64_t off = FP8 ? (uint64_t)(k * 2) : (uint64_t)((k >> 2) * (Cfg::kSlabBytes >> 4) + (k & 3) * 2);
+            if (FP8) umma_f8_ss(tS[i & 1], q_desc + off, kd + off, idesc_qk, k > 0);
+            else umma_f16_ss(tS[i & 1], q_desc + off, kd + off, idesc_qk, k > 0);
           }
           umma_commit(BAR(kKvEmpty + stage));
           umma_commit(BAR(kSFull + (i & 1)));
@@ -310,18 +340,20 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const int s = i & 1;
         const uint32_t stage = kv_cnt % NS;
         const uint32_t ph = (kv_cnt / NS) & 1;
+        PT_MARK(0)
         if (!mbar_wait(BAR(kKvFull + stage), ph, wctx, 202)) return false;
+        PT_MARK(3)
         if (!mbar_wait(BAR(kPFull + s), p_cnt[s] & 1, wctx, 203)) return false;
+        PT_MARK(4)
         ++p_cnt[s];
         tc_fence_after();
         if (lane == 0) {
-          const uint32_t b0 = smem_u32(sKV + stage * Cfg::kTileBytes);
+          const uint64_t vd = v_desc0 + (uint64_t)stage * (Cfg::kTileBytes >> 4);
 #pragma unroll
           for (int k = 0; k < Cfg::kKSteps; ++k) {
             // V is MN-major: one k step = kMmaK token rows of 128 B; the second 64-channel slab of a
             // bf16 tile is reached through the leading byte offset.
-            const uint64_t db = umma_desc_sw128(b0 + (uint32_t)k * (Cfg::kMmaK * 128u),
-                                                FP8 ? 0u : (uint32_t)Cfg::kSlabBytes, 1024);
+            const uint64_t db = vd + (uint64_t)(k * ((Cfg::kMmaK * 128) >> 4));
             const uint32_t a_t = tS[s] + (uint32_t)k * Cfg::kPColsPerStep;
             if (FP8) umma_f8_ts(tO[s], a_t, db, idesc_pv, (i >= 2) || (k > 0));
             else umma_f16_ts(tO[s], a_t, db, idesc_pv, (i >= 2) || (k > 0));
@@ -342,8 +374,11 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (ok && lane == 0) umma_commit(BAR(kOFinal));
       __syncwarp();
     }
+    PT_MARK(0)
+    PT_FLUSH(32)
   } else if (warp < 8) {
     // ===================================== softmax + epilogue ===================================
+    setmaxnreg_inc<216>();
     const int grp = warp >> 2;                 // stream owned by this group
     const int row = threadIdx.x & 127;         // query row inside the tile = tensor-memory lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
@@ -353,6 +388,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const bool need_mask_meta = (p.block_sizes != nullptr) || (p.Sk % BLK != 0);
     constexpr float kRescaleThreshold = FP8 ? 1.8073549f /* log2(448/128) */ : 8.0f;
     constexpr float kPBias = FP8 ? 7.0f : 0.0f;
+    PT_DECL
 
     for (int w = blockIdx.x; w < p.num_work && ok; w += gridDim.x) {
       const WorkItem t = decode_work<BLK>(p, w);
@@ -405,8 +441,10 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
         }
 
+        PT_MARK(0)
         ok = mbar_wait(BAR(kSFull + grp), s_cnt & 1, wctx, 300 + grp);
         if (!ok) break;
+        PT_MARK(1)
         ++s_cnt;
         tc_fence_after();
         if (!row_active) {
@@ -416,51 +454,85 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           continue;
         }
         float sv[128];
-        {
-          uint32_t* su = reinterpret_cast<uint32_t*>(sv);
-          tmem_ld32(tS[grp] + lane_base + 0, su + 0);
-          tmem_ld32(tS[grp] + lane_base + 32, su + 32);
-          tmem_ld32(tS[grp] + lane_base + 64, su + 64);
-          tmem_ld32(tS[grp] + lane_base + 96, su + 96);
-          tmem_wait_ld();
-        }
-        // ---- mask
-        if (BLK == 128) {
-          if (len0 < 128) {
-#pragma unroll
-            for (int c = 0; c < 128; ++c) sv[c] = (c < len0) ? sv[c] : -INFINITY;
-          }
-        } else {
-          if (len0 < 64 || len1 < 64) {
-#pragma unroll
-            for (int c = 0; c < 64; ++c) sv[c] = (c < len0) ? sv[c] : -INFINITY;
-#pragma unroll
-            for (int c = 0; c < 64; ++c) sv[64 + c] = (c < len1) ? sv[64 + c] : -INFINITY;
-          }
-        }
-        // ---- block max in the scaled log2 domain
+        uint32_t* su = reinterpret_cast<uint32_t*>(sv);
+        const uint32_t t_row = tS[grp] + lane_base;
+        const bool masked = (BLK == 128) ? (len0 < 128) : (len0 < 64 || len1 < 64);  // warp-uniform
         float bm;
-        if (FP8) {
-          bm = -INFINITY;
+        if (FP8 || masked) {
+          tmem_ld32(t_row + 0, su + 0);
+          tmem_ld32(t_row + 32, su + 32);
+          tmem_ld32(t_row + 64, su + 64);
+          tmem_ld32(t_row + 96, su + 96);
+          tmem_wait_ld();
+          PT_MARK(2)
+          if (masked) {
+            if (BLK == 128) {
 #pragma unroll
-          for (int g = 0; g < 8; ++g) {
-            float gm = sv[g * 16];
+              for (int c = 0; c < 128; ++c) sv[c] = (c < len0) ? sv[c] : -INFINITY;
+            } else {
 #pragma unroll
-            for (int c = 1; c < 16; ++c) gm = fmaxf(gm, sv[g * 16 + c]);
-            // -inf * 0 would be NaN for fully masked groups beyond the sequence end
-            const float scaled = (gm == -INFINITY) ? -INFINITY : gm * ksc[g];
-            bm = fmaxf(bm, scaled);
+              for (int c = 0; c < 64; ++c) sv[c] = (c < len0) ? sv[c] : -INFINITY;
+#pragma unroll
+              for (int c = 0; c < 64; ++c) sv[64 + c] = (c < len1) ? sv[64 + c] : -INFINITY;
+            }
+          }
+          // ---- block max in the scaled log2 domain
+          if (FP8) {
+            bm = -INFINITY;
+#pragma unroll
+            for (int g = 0; g < 8; ++g) {
+              float gm = sv[g * 16];
+#pragma unroll
+              for (int c = 1; c < 16; c += 2) gm = fmax3(gm, sv[g * 16 + c], sv[g * 16 + ((c + 1) & 15)]);
+              // -inf * 0 would be NaN for fully masked groups beyond the sequence end
+              const float scaled = (gm == -INFINITY) ? -INFINITY : gm * ksc[g];
+              bm = fmaxf(bm, scaled);
+            }
+          } else {
+            float m0 = sv[0], m1 = sv[1];
+#pragma unroll
+            for (int c = 2; c < 128; c += 4) {
+              m0 = fmax3(m0, sv[c], sv[c + 1]);
+              m1 = fmax3(m1, sv[(c + 2) & 127], sv[(c + 3) & 127]);
+            }
+            bm = fmaxf(m0, m1) * p.scale_log2;
           }
         } else {
-          float m0 = sv[0], m1 = sv[1], m2 = sv[2], m3 = sv[3];
+          // common case: the 32-column chunks arrive while the maximum of the previous one is taken
+          float m0, m1;
+          tmem_ld32(t_row + 0, su + 0);
+          tmem_wait_ld();
+          tmem_ld32(t_row + 32, su + 32);
+          m0 = fmax3(sv[0], sv[1], sv[2]);
+          m1 = fmax3(sv[3], sv[4], sv[5]);
 #pragma unroll
-          for (int c = 4; c < 128; c += 4) {
-            m0 = fmaxf(m0, sv[c]);
-            m1 = fmaxf(m1, sv[c + 1]);
-            m2 = fmaxf(m2, sv[c + 2]);
-            m3 = fmaxf(m3, sv[c + 3]);
+          for (int c = 6; c < 30; c += 4) {
+            m0 = fmax3(m0, sv[c], sv[c + 1]);
+            m1 = fmax3(m1, sv[c + 2], sv[c + 3]);
           }
-          bm = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3)) * p.scale_log2;
+          m0 = fmax3(m0, sv[30], sv[31]);
+          tmem_wait_ld();
+          tmem_ld32(t_row + 64, su + 64);
+#pragma unroll
+          for (int c = 32; c < 64; c += 4) {
+            m0 = fmax3(m0, sv[c], sv[c + 1]);
+            m1 = fmax3(m1, sv[c + 2], sv[c + 3]);
+          }
+          tmem_wait_ld();
+          tmem_ld32(t_row + 96, su + 96);
+#pragma unroll
+          for (int c = 64; c < 96; c += 4) {
+            m0 = fmax3(m0, sv[c], sv[c + 1]);
+            m1 = fmax3(m1, sv[c + 2], sv[c + 3]);
+          }
+          tmem_wait_ld();
+          PT_MARK(2)
+#pragma unroll
+          for (int c = 96; c < 128; c += 4) {
+            m0 = fmax3(m0, sv[c], sv[c + 1]);
+            m1 = fmax3(m1, sv[c + 2], sv[c + 3]);
+          }
+          bm = fmaxf(m0, m1) * p.scale_log2;
         }
         const float m_new = fmaxf(m_cur, bm);
         const bool first = (i == grp);
@@ -488,6 +560,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         const float m_used = (m_cur == -INFINITY) ? 0.f : m_cur;
         const float neg_m = kPBias - m_used;
+        PT_MARK(3)
         // ---- exponentials, row sum, P to tensor memory
         float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
         if (FP8) {
@@ -509,34 +582,48 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             tmem_st8(tS[grp] + lane_base + c4 * 8, pk);
           }
         } else {
+          const uint64_t sc2 = pack2(p.scale_log2, p.scale_log2);
+          const uint64_t nm2 = pack2(neg_m, neg_m);
+          uint64_t s0 = pack2(0.f, 0.f), s1 = s0;
 #pragma unroll
           for (int c4 = 0; c4 < 4; ++c4) {
             uint32_t pk[16];
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
               const int c = c4 * 32 + e * 2;
-              const float x0 = ex2_approx(fmaf(sv[c], p.scale_log2, neg_m));
-              const float x1 = ex2_approx(fmaf(sv[c + 1], p.scale_log2, neg_m));
-              if (e & 1) { a2 += x0; a3 += x1; } else { a0 += x0; a1 += x1; }
+              float x0, x1;
+              unpack2(ffma2(pack2(sv[c], sv[c + 1]), sc2, nm2), x0, x1);
+              x0 = ex2_approx(x0);
+              x1 = ex2_approx(x1);
+              if (e & 1) s1 = fadd2(s1, pack2(x0, x1));
+              else s0 = fadd2(s0, pack2(x0, x1));
               pk[e] = pack_bf16x2(x0, x1);
             }
             tmem_st16(tS[grp] + lane_base + c4 * 16, pk);
           }
+          float y0, y1, y2, y3;
+          unpack2(s0, y0, y1);
+          unpack2(s1, y2, y3);
+          a0 = y0; a1 = y1; a2 = y2; a3 = y3;
         }
         l_sum += (a0 + a1) + (a2 + a3);
+        PT_MARK(4)
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(BAR(kPFull + grp));
+        PT_MARK(5)
       }
       if (!ok) break;
 
       // ------------------------------------ tile epilogue ------------------------------------
+      PT_MARK(0)
       if (n_it > 0) {
         ok = mbar_wait(BAR(kOFinal), of_cnt & 1, wctx, 310 + grp);
         if (!ok) break;
         ++of_cnt;
         tc_fence_after();
       }
+      PT_MARK(6)
       s_stats[grp][row] = make_float2(m_cur, l_sum);
       ok = mbar_rendezvous(BAR(kEpiA), epi_a, wctx, 320);
       if (!ok) break;
@@ -624,7 +711,11 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
     }
+    PT_MARK(7)
     if ((threadIdx.x & 127) == 0 && !SPLIT) tma_store_wait_all<0>();
+    if ((warp & 3) == 0) { PT_FLUSH(grp * 8) }
+  } else {
+    setmaxnreg_dec<56>();
   }
 
   // ------------------------------------------ teardown ------------------------------------------
