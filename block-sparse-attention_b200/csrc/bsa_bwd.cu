@@ -121,31 +121,34 @@ __device__ __forceinline__ void store_row_half(__nv_bfloat16* dst, const uint32_
 constexpr uint32_t kIdescKK = umma_idesc(1, 1, 0, 0, 128, 128);   // A K-major, B K-major
 constexpr uint32_t kIdescKMN = umma_idesc(1, 1, 0, 1, 128, 128);  // A K-major (smem or tmem), B MN-major
 
+// The helpers below take ready-made descriptors (built once per kernel); a byte offset b inside a tile is
+// an addition of b >> 4 to the descriptor's low word.
+__device__ __forceinline__ uint64_t desc_k_major(uint32_t saddr) { return umma_desc_sw128(saddr, 0, 1024); }
+__device__ __forceinline__ uint64_t desc_mn_major(uint32_t saddr) { return umma_desc_sw128(saddr, kSlab, 1024); }
+constexpr uint64_t kTileDescStep = kTile >> 4;  // descriptor distance between consecutive ring tiles
+
 // D = A(smem, K-major) * B(smem, K-major)^T over the 128-deep contraction: 8 k-steps across two slabs
-__device__ __forceinline__ void mma_ss_kk(uint32_t d, uint32_t a_base, uint32_t b_base, bool acc) {
+__device__ __forceinline__ void mma_ss_kk(uint32_t d, uint64_t a_desc, uint64_t b_desc, bool acc) {
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
-    const uint32_t off = (uint32_t)(k >> 2) * kSlab + (uint32_t)(k & 3) * 32u;
-    umma_f16_ss(d, umma_desc_sw128(a_base + off, 0, 1024), umma_desc_sw128(b_base + off, 0, 1024), kIdescKK,
-                (acc || k > 0) ? 1u : 0u);
+    const uint64_t off = (uint64_t)((k >> 2) * (kSlab >> 4) + (k & 3) * 2);
+    umma_f16_ss(d, a_desc + off, b_desc + off, kIdescKK, (acc || k > 0) ? 1u : 0u);
   }
 }
 // D (+)= A(smem, K-major [rows][contraction]) * B(smem tile [contraction rows][128 channels], MN-major)
-__device__ __forceinline__ void mma_ss_kmn(uint32_t d, uint32_t a_base, uint32_t b_base, bool acc) {
+__device__ __forceinline__ void mma_ss_kmn(uint32_t d, uint64_t a_desc, uint64_t b_desc_mn, bool acc) {
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
-    const uint32_t aoff = (uint32_t)(k >> 2) * kSlab + (uint32_t)(k & 3) * 32u;
-    umma_f16_ss(d, umma_desc_sw128(a_base + aoff, 0, 1024),
-                umma_desc_sw128(b_base + (uint32_t)k * 2048u, kSlab, 1024), kIdescKMN, (acc || k > 0) ? 1u : 0u);
+    const uint64_t aoff = (uint64_t)((k >> 2) * (kSlab >> 4) + (k & 3) * 2);
+    umma_f16_ss(d, a_desc + aoff, b_desc_mn + (uint64_t)(k * 128), kIdescKMN, (acc || k > 0) ? 1u : 0u);
   }
 }
 // D (+)= A(tmem bf16, two 32-column halves at a_lo / a_hi) * B(smem MN-major)
-__device__ __forceinline__ void mma_ts_kmn(uint32_t d, uint32_t a_lo, uint32_t a_hi, uint32_t b_base, bool acc) {
+__device__ __forceinline__ void mma_ts_kmn(uint32_t d, uint32_t a_lo, uint32_t a_hi, uint64_t b_desc_mn, bool acc) {
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     const uint32_t a = (k < 4) ? (a_lo + (uint32_t)k * 8u) : (a_hi + (uint32_t)(k - 4) * 8u);
-    umma_f16_ts(d, a, umma_desc_sw128(b_base + (uint32_t)k * 2048u, kSlab, 1024), kIdescKMN,
-                (acc || k > 0) ? 1u : 0u);
+    umma_f16_ts(d, a, b_desc_mn + (uint64_t)(k * 128), kIdescKMN, (acc || k > 0) ? 1u : 0u);
   }
 }
 
@@ -254,6 +257,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     uint32_t r_cnt = 0, q_cnt = 0, ds_cnt = 0, free_cnt = 0;
     bool ok = true;
     bool first_tile = true;
+    const uint64_t dq_desc = desc_k_major(smem_u32(sQ)), ddo_desc = desc_k_major(smem_u32(sdO));
+    const uint64_t ring_k = desc_k_major(smem_u32(sRing)), ring_mn = desc_mn_major(smem_u32(sRing));
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
       const int n = row_count(w);
       if (n == 0) continue;
@@ -270,7 +275,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (!wait_full(base + 2 * j)) return false;
         tc_fence_after();
         if (lane == 0) {
-          mma_ss_kk(tS[j & 1], smem_u32(sQ), smem_u32(sRing + stage_of(base + 2 * j) * kTile), false);
+          mma_ss_kk(tS[j & 1], dq_desc, ring_k + stage_of(base + 2 * j) * kTileDescStep, false);
           umma_commit(BAR(kSFull + (j & 1)));
         }
         __syncwarp();
@@ -280,7 +285,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (!wait_full(base + 2 * j + 1)) return false;
         tc_fence_after();
         if (lane == 0) {
-          mma_ss_kk(tdP, smem_u32(sdO), smem_u32(sRing + stage_of(base + 2 * j + 1) * kTile), false);
+          mma_ss_kk(tdP, ddo_desc, ring_k + stage_of(base + 2 * j + 1) * kTileDescStep, false);
           umma_commit(BAR(kDpFull));
         }
         __syncwarp();
@@ -306,7 +311,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (lane == 0) {
           const uint32_t sk = stage_of(base + 2 * j), sv = stage_of(base + 2 * j + 1);
           // dQ += dS_j (staged in the V_j slot, K-major) * K_j (MN-major view of the K tile)
-          mma_ss_kmn(tdQ, smem_u32(sRing + sv * kTile), smem_u32(sRing + sk * kTile), j > 0);
+          mma_ss_kmn(tdQ, ring_k + sv * kTileDescStep, ring_mn + sk * kTileDescStep, j > 0);
           umma_commit(BAR(kREmpty + sk));
           umma_commit(BAR(kREmpty + sv));
         }
@@ -542,6 +547,8 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   } else if (warp == kBwdMmaWarp) {
     uint32_t r_cnt = 0, kv_cnt = 0, p_cnt = 0, ds_cnt = 0, free_cnt = 0;
     bool ok = true, first_item = true;
+    const uint64_t k_desc = desc_k_major(smem_u32(sK)), v_desc = desc_k_major(smem_u32(sV));
+    const uint64_t ring_k = desc_k_major(smem_u32(sRing)), ring_mn = desc_mn_major(smem_u32(sRing));
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
       const int nb = w % p.Nkv;
       const int bh = w / p.Nkv;
@@ -559,7 +566,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (!wait_full(base + 2 * i)) return false;
         tc_fence_after();
         if (lane == 0) {
-          mma_ss_kk(tS, smem_u32(sK), smem_u32(sRing + stage_of(base + 2 * i) * kTile), false);
+          mma_ss_kk(tS, k_desc, ring_k + stage_of(base + 2 * i) * kTileDescStep, false);
           umma_commit(BAR(kSFull));
         }
         __syncwarp();
@@ -569,7 +576,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (!wait_full(base + 2 * i + 1)) return false;
         tc_fence_after();
         if (lane == 0) {
-          mma_ss_kk(tdP, smem_u32(sV), smem_u32(sRing + stage_of(base + 2 * i + 1) * kTile), false);
+          mma_ss_kk(tdP, v_desc, ring_k + stage_of(base + 2 * i + 1) * kTileDescStep, false);
           umma_commit(BAR(kDpFull));
         }
         __syncwarp();
@@ -589,7 +596,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         tc_fence_after();
         if (lane == 0) {
           const uint32_t sd = stage_of(base + 2 * i + 1);
-          mma_ts_kmn(tdV, tS, tS + 64u, smem_u32(sRing + sd * kTile), i > 0);  // dV += P^T dO_i
+          mma_ts_kmn(tdV, tS, tS + 64u, ring_mn + sd * kTileDescStep, i > 0);  // dV += P^T dO_i
           umma_commit(BAR(kREmpty + sd));
         }
         __syncwarp();
@@ -603,7 +610,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         tc_fence_after();
         if (lane == 0) {
           const uint32_t sq = stage_of(base + 2 * i);
-          mma_ts_kmn(tdK, tdP, tdP + 64u, smem_u32(sRing + sq * kTile), i > 0);  // dK += dS^T Q_i
+          mma_ts_kmn(tdK, tdP, tdP + 64u, ring_mn + sq * kTileDescStep, i > 0);  // dK += dS^T Q_i
           umma_commit(BAR(kREmpty + sq));
         }
         __syncwarp();
