@@ -23,6 +23,13 @@
 #include "bsa_common.cuh"
 #include "bsa_host.h"
 
+#ifdef BSA_PHASE_TIMERS
+__device__ unsigned long long g_bwd_prof[128];
+#define PTB_FLUSH(base) PT_FLUSH_TO(g_bwd_prof, base)
+#else
+#define PTB_FLUSH(base)
+#endif
+
 namespace bsa {
 
 constexpr int kBwdThreads = 320;
@@ -259,17 +266,23 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     bool first_tile = true;
     const uint64_t dq_desc = desc_k_major(smem_u32(sQ)), ddo_desc = desc_k_major(smem_u32(sdO));
     const uint64_t ring_k = desc_k_major(smem_u32(sRing)), ring_mn = desc_mn_major(smem_u32(sRing));
+    PT_DECL
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
       const int n = row_count(w);
       if (n == 0) continue;
+      PT_MARK(0)
       ok = mbar_wait(BAR(kQFull), q_cnt & 1, wctx, 410);
       if (!ok) break;
+      PT_MARK(1)
       ++q_cnt;
       tc_fence_after();
       const uint32_t base = r_cnt;  // ring position of K_0 of this tile; K_j at base+2j, V_j at base+2j+1
       auto stage_of = [&](uint32_t pos) { return pos % NS; };
       auto wait_full = [&](uint32_t pos) {
-        return mbar_wait(BAR(kRFull + stage_of(pos)), (pos / NS) & 1, wctx, 411);
+        PT_MARK(0)
+        const bool r = mbar_wait(BAR(kRFull + stage_of(pos)), (pos / NS) & 1, wctx, 411);
+        PT_MARK(2)
+        return r;
       };
       auto issue_s = [&](int j) -> bool {
         if (!wait_full(base + 2 * j)) return false;
@@ -295,16 +308,20 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (ok) ok = issue_dp(0);
       if (ok && n > 1) ok = issue_s(1);
       for (int j = 0; j < n && ok; ++j) {
+        PT_MARK(0)
         ok = mbar_wait(BAR(kDsFull), ds_cnt & 1, wctx, 412);  // dS_j staged, dP and S_j consumed
         if (!ok) break;
+        PT_MARK(3)
         ++ds_cnt;
         if (j + 1 < n) {
           ok = issue_dp(j + 1);
           if (!ok) break;
         }
         if (j == 0 && !first_tile) {  // the previous tile's epilogue has drained dQ
+          PT_MARK(0)
           ok = mbar_wait(BAR(kDqFree), free_cnt & 1, wctx, 413);
           if (!ok) break;
+          PT_MARK(4)
           ++free_cnt;
         }
         tc_fence_after();
@@ -327,12 +344,15 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       r_cnt += 2 * n;
       first_tile = false;
     }
+    PT_MARK(0)
+    PTB_FLUSH(16)
   } else if (warp < 8) {
     const int grp = warp >> 2;
     const int row = threadIdx.x & 127;
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     uint32_t r_cnt = 0, s_cnt[2] = {0, 0}, dp_cnt = 0, fin_cnt = 0;
     bool ok = true;
+    PT_DECL
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
       const int n = row_count(w);
       const int m = w % p.Nq;
@@ -358,8 +378,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         int len = p.Sk - blk * 128;
         len = (blk < 0 || blk >= p.Nkv) ? 0 : min(len, 128);
         // ---- phase 1: P = exp2(S*scale - lse)
+        PT_MARK(0)
         ok = mbar_wait(BAR(kSFull + (j & 1)), s_cnt[j & 1] & 1, wctx, 420);
         if (!ok) break;
+        PT_MARK(1)
         ++s_cnt[j & 1];
         tc_fence_after();
         float pr[64];
@@ -377,8 +399,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           for (int c = 0; c < 64; ++c) pr[c] = (grp * 64 + c < len) ? pr[c] : 0.f;
         }
         // ---- phase 2: dS = P o (dP - delta) -> bf16 -> shared memory (the V_j slot, K-major, swizzled)
+        PT_MARK(2)
         ok = mbar_wait(BAR(kDpFull), dp_cnt & 1, wctx, 421);
         if (!ok) break;
+        PT_MARK(3)
         ++dp_cnt;
         tc_fence_after();
         uint32_t dp[64];
@@ -401,6 +425,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(BAR(kDsFull));
+        PT_MARK(4)
       }
       if (!ok) break;
       r_cnt += 2 * n;
@@ -416,7 +441,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       tc_fence_before();
       mbar_arrive(BAR(kDqFree));
       if (seq < p.Sq) store_row_half(dq_row, acc, p.softmax_scale);
+      PT_MARK(5)
     }
+    if ((warp & 3) == 0) { PTB_FLUSH(grp * 8) }
   }
   tc_fence_before();
   __syncthreads();
@@ -549,6 +576,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     bool ok = true, first_item = true;
     const uint64_t k_desc = desc_k_major(smem_u32(sK)), v_desc = desc_k_major(smem_u32(sV));
     const uint64_t ring_k = desc_k_major(smem_u32(sRing)), ring_mn = desc_mn_major(smem_u32(sRing));
+    PT_DECL
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
       const int nb = w % p.Nkv;
       const int bh = w / p.Nkv;
@@ -560,7 +588,10 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const uint32_t base = r_cnt;  // Q_i at base+2i, dO_i at base+2i+1
       auto stage_of = [&](uint32_t pos) { return pos % NS; };
       auto wait_full = [&](uint32_t pos) {
-        return mbar_wait(BAR(kRFull + stage_of(pos)), (pos / NS) & 1, wctx, 511);
+        PT_MARK(0)
+        const bool r = mbar_wait(BAR(kRFull + stage_of(pos)), (pos / NS) & 1, wctx, 511);
+        PT_MARK(2)
+        return r;
       };
       auto issue_s = [&](int i) -> bool {  // S^T = K Q_i^T
         if (!wait_full(base + 2 * i)) return false;
@@ -585,8 +616,10 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       ok = issue_s(0);
       if (ok) ok = issue_dp(0);
       for (int i = 0; i < T && ok; ++i) {
+        PT_MARK(0)
         ok = mbar_wait(BAR(kPFull), p_cnt & 1, wctx, 512);  // P^T_i in tensor memory
         if (!ok) break;
+        PT_MARK(3)
         ++p_cnt;
         if (i == 0 && !first_item) {  // previous item's epilogue has drained dV / dK
           ok = mbar_wait(BAR(kFree), free_cnt & 1, wctx, 513);
@@ -604,8 +637,10 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           ok = issue_s(i + 1);
           if (!ok) break;
         }
+        PT_MARK(0)
         ok = mbar_wait(BAR(kDsFull), ds_cnt & 1, wctx, 514);  // dS^T_i in tensor memory
         if (!ok) break;
+        PT_MARK(4)
         ++ds_cnt;
         tc_fence_after();
         if (lane == 0) {
@@ -625,12 +660,15 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       r_cnt += 2 * T;
       first_item = false;
     }
+    PT_MARK(0)
+    PTB_FLUSH(64 + 16)
   } else if (warp < 8) {
     const int grp = warp >> 2;
     const int row = threadIdx.x & 127;  // kv token inside the block = tensor-memory lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     uint32_t s_cnt = 0, dp_cnt = 0, fin_cnt = 0, tile_cnt = 0, r_cnt = 0;
     bool ok = true;
+    PT_DECL
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
       const int nb = w % p.Nkv;
       const int bh = w / p.Nkv;
@@ -657,8 +695,10 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const float4* st_d = reinterpret_cast<const float4*>(sStats + (tile_cnt % kStatSlots) * 256 + 128 + grp * 64);
         ++tile_cnt;
         // ---- phase 1: P^T = exp2(S^T*scale - lse[q]) -> bf16 -> tensor memory (head of this group's S half)
+        PT_MARK(0)
         ok = mbar_wait(BAR(kSFull), s_cnt & 1, wctx, 520);
         if (!ok) break;
+        PT_MARK(1)
         ++s_cnt;
         {
           // observe the arrival of this tile's row statistics directly (they were copied on the Q
@@ -696,9 +736,11 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         tc_fence_before();
         mbar_arrive(BAR(kPFull));
+        PT_MARK(2)
         // ---- phase 2: dS^T = P^T o (dP^T - delta[q]) -> bf16 -> tensor memory
         ok = mbar_wait(BAR(kDpFull), dp_cnt & 1, wctx, 521);
         if (!ok) break;
+        PT_MARK(3)
         ++dp_cnt;
         tc_fence_after();
         uint32_t dp[64];
@@ -722,6 +764,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         tc_fence_before();
         mbar_arrive(BAR(kDsFull));
+        PT_MARK(4)
       }
       if (!ok) break;
       // ---- epilogue
@@ -740,7 +783,9 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       tc_fence_before();
       mbar_arrive(BAR(kFree));
       if (kv_valid) store_row_half(dk_row, acc, p.softmax_scale);
+      PT_MARK(5)
     }
+    if ((warp & 3) == 0) { PTB_FLUSH(64 + grp * 8) }
   }
   tc_fence_before();
   __syncthreads();
@@ -753,6 +798,17 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 }  // namespace bsa
 
 using namespace bsa;
+
+#ifdef BSA_PHASE_TIMERS
+// development builds only: copies the backward phase counters to the host and clears them
+extern "C" int bsa_debug_read_bwd_prof(unsigned long long* host_out) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(host_out, g_bwd_prof, sizeof(unsigned long long) * 128);
+  static unsigned long long zeros[128];
+  cudaMemcpyToSymbol(g_bwd_prof, zeros, sizeof(zeros));
+  return 0;
+}
+#endif
 
 extern "C" int64_t bsa_bwd_workspace_bytes(int32_t B, int32_t H, int32_t Sq, int32_t Sk, int32_t D) {
   (void)Sk;

@@ -13,6 +13,21 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+// Optional per-role phase timers (development aid, compiled out unless BSA_PHASE_TIMERS is defined):
+// lane 0 of one warp per role accumulates clock64() deltas into eight buckets and adds them to a
+// caller-provided buffer of unsigned 64-bit counters.
+#ifdef BSA_PHASE_TIMERS
+#define PT_DECL unsigned long long pt_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; unsigned long long pt_t = clock64();
+#define PT_MARK(i) { const unsigned long long pt_n = clock64(); pt_acc[i] += pt_n - pt_t; pt_t = pt_n; }
+#define PT_FLUSH_TO(ptr, base) if (lane == 0 && (ptr) != nullptr) { \
+    unsigned long long* pt_g = (ptr); \
+    for (int pt_i = 0; pt_i < 8; ++pt_i) atomicAdd(pt_g + (base) + pt_i, pt_acc[pt_i]); }
+#else
+#define PT_DECL
+#define PT_MARK(i)
+#define PT_FLUSH_TO(ptr, base)
+#endif
+
 namespace bsa {
 
 // ---------------------------------------------------------------------------------------------
@@ -385,6 +400,33 @@ __device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
+// 2^x for a packed pair on the FMA pipe instead of the special-function unit: x is clamped to >= -127,
+// split into floor and fraction with the 2^23+2^22 round-down trick, the fraction goes through a
+// degree-3 polynomial (max relative error 8.8e-5, far below the bf16 rounding of the result) and the
+// integer part is added into the exponent field.
+__device__ __forceinline__ uint64_t ex2_emu2(float x0, float x1) {
+  x0 = fmaxf(x0, -127.f);
+  x1 = fmaxf(x1, -127.f);
+  const uint64_t x = pack2(x0, x1);
+  const uint64_t magic = pack2(12582912.f, 12582912.f);
+  uint64_t t;
+  asm("add.rm.ftz.f32x2 %0, %1, %2;" : "=l"(t) : "l"(x), "l"(magic));
+  uint64_t r;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(t), "l"(magic));
+  uint64_t f;
+  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(f) : "l"(x), "l"(r));
+  uint64_t pl = ffma2(f, pack2(0.077119089663028717041015625f, 0.077119089663028717041015625f),
+                      pack2(0.227564394474029541015625f, 0.227564394474029541015625f));
+  pl = ffma2(pl, f, pack2(0.695146143436431884765625f, 0.695146143436431884765625f));
+  pl = ffma2(pl, f, pack2(1.f, 1.f));
+  float t0, t1, p0, p1;
+  unpack2(t, t0, t1);
+  unpack2(pl, p0, p1);
+  const uint32_t r0 = __float_as_uint(p0) + (__float_as_uint(t0) << 23);
+  const uint32_t r1 = __float_as_uint(p1) + (__float_as_uint(t1) << 23);
+  return pack2(__uint_as_float(r0), __uint_as_float(r1));
+}
+
 // register re-partitioning between warpgroups (every warp of the warpgroup must execute it)
 template <int N>
 __device__ __forceinline__ void setmaxnreg_inc() {

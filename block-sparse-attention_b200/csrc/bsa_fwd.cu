@@ -4,9 +4,9 @@
 // One persistent CTA per SM walks (q tile, split) work items.  Warp roles:
 //   warps 0-3  softmax group 0: owns stream 0 (KV iterations 0, 2, 4, ...), one thread per query row
 //   warps 4-7  softmax group 1: owns stream 1 (KV iterations 1, 3, 5, ...)
-//   warp  8    MMA issue (one lane)
-//   warp  9    TMA producer (one lane)
-//   warps 10-11 idle: they complete the third warpgroup so that registers can be re-partitioned
+//   warps 8-9  MMA issue, one warp (one lane) per stream
+//   warp  10   TMA producer (one lane)
+//   warp  11   idle: it completes the third warpgroup so that registers can be re-partitioned
 //              (setmaxnreg) in favour of the softmax groups
 // Tensor memory (512 columns): S0 @0, S1 @128, O0 @256, O1 @384 (fp32, 128 lanes x 128 columns each);
 // the probabilities P_s overwrite the head of S_s (bf16: 64 columns, e4m3: 32 columns) and are the
@@ -25,20 +25,9 @@
 #include "bsa_common.cuh"
 #include "bsa_host.h"
 
-// Optional per-role phase timers (development aid, compiled out unless BSA_PHASE_TIMERS is defined):
-// lane 0 of one warp per role accumulates clock64() deltas and adds them to a caller buffer of 64 u64
-// passed in the otherwise unused partial_lse pointer of an unsplit launch.
-#ifdef BSA_PHASE_TIMERS
-#define PT_DECL unsigned long long pt_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}; unsigned long long pt_t = clock64();
-#define PT_MARK(i) { const unsigned long long pt_n = clock64(); pt_acc[i] += pt_n - pt_t; pt_t = pt_n; }
-#define PT_FLUSH(base) if (lane == 0 && p.partial_lse != nullptr) { \
-    unsigned long long* pt_g = reinterpret_cast<unsigned long long*>(p.partial_lse); \
-    for (int pt_i = 0; pt_i < 8; ++pt_i) atomicAdd(pt_g + (base) + pt_i, pt_acc[pt_i]); }
-#else
-#define PT_DECL
-#define PT_MARK(i)
-#define PT_FLUSH(base)
-#endif
+// Phase timers (development aid, see bsa_common.cuh): the 64-slot buffer of an unsplit launch travels in
+// the otherwise unused partial_lse pointer.
+#define PT_FLUSH(base) PT_FLUSH_TO(reinterpret_cast<unsigned long long*>(p.partial_lse), base)
 
 namespace bsa {
 
@@ -62,10 +51,17 @@ struct FwdParams {
   float scale_log2;
 };
 
-constexpr int kThreads = 384;  // warps 10-11 only give their registers away
+// Of every eight column pairs of a softmax row, this many take the polynomial exp2 on the FMA pipe
+// instead of the special-function unit.  Measured on B200 (cfg2 forward): 0 -> 3.73 ms, 1 -> 3.87 ms,
+// 2 -> 3.97 ms, 4 -> 4.30 ms: the kernel is bound by its dependency chain, not by the SFU, so it is off.
+#ifndef BSA_EX2_EMU8
+#define BSA_EX2_EMU8 0
+#endif
+
+constexpr int kThreads = 384;  // warp 11 only gives its registers away
 constexpr int kSoftmaxThreads = 256;
 constexpr int kMmaWarp = 8;
-constexpr int kLoadWarp = 9;
+constexpr int kLoadWarp = 10;  // warps 8 and 9 issue the MMAs of stream 0 and 1
 
 
 template <bool FP8>
@@ -152,7 +148,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   auto BAR = [&](int i) { return bar_base + (uint32_t)i * 8u; };
   constexpr int kQFull = 0, kQEmpty = 1, kKvFull = 2, kKvEmpty = 2 + NS, kSFull = 2 + 2 * NS,
                 kPFull = kSFull + 2, kOFinal = kPFull + 2, kEpiA = kOFinal + 1, kEpiB = kEpiA + 1,
-                kGrpA = kEpiB + 1, kGrpB = kGrpA + 2, kNumBars = kGrpB + 2;
+                kGrpA = kEpiB + 1, kGrpB = kGrpA + 2, kPHalf = kGrpB + 2, kNumBars = kPHalf + 2;
   float2 (*s_stats)[128] = reinterpret_cast<float2 (*)[128]>(bars + 32);  // [2][128] (max, sum)
   uint32_t& s_tmem_base = *reinterpret_cast<uint32_t*>(bars + 32 + 256);
   volatile int& s_abort = *reinterpret_cast<volatile int*>(bars + 32 + 256 + 1);
@@ -168,16 +164,18 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   if (threadIdx.x == 0) {
     s_abort = 0;
     mbar_init(BAR(kQFull), 1);
-    mbar_init(BAR(kQEmpty), 1);
+    mbar_init(BAR(kQEmpty), 2);
     for (int i = 0; i < NS; ++i) {
       mbar_init(BAR(kKvFull + i), 1);
       mbar_init(BAR(kKvEmpty + i), 1);
     }
     for (int s = 0; s < 2; ++s) {
       mbar_init(BAR(kSFull + s), 1);
+      // every softmax thread arrives itself: measured faster than one elected arrival per warp
       mbar_init(BAR(kPFull + s), 128);
+      mbar_init(BAR(kPHalf + s), 128);
     }
-    mbar_init(BAR(kOFinal), 1);
+    mbar_init(BAR(kOFinal), 2);
     mbar_init(BAR(kEpiA), kSoftmaxThreads);
     mbar_init(BAR(kEpiB), kSoftmaxThreads);
     for (int s = 0; s < 2; ++s) {
@@ -286,14 +284,18 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
     }
     PT_FLUSH(48)
-  } else if (warp == kMmaWarp) {
+  } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
     // ========================================= MMA issue ========================================
+    // One issuing warp per stream.  tcgen05.mma issue stalls the issuing thread at the execution rate,
+    // so with a single issuer the tensor pipe idles during every barrier wait and commit; with two
+    // issuers one stream's bookkeeping overlaps the other stream's MMAs.  Per stream the order
+    // PV(i) -> QK(i+2) is program order of one thread, which is what the aliasing of P_s with S_s needs.
     setmaxnreg_dec<56>();
+    const int s = warp - kMmaWarp;
     constexpr uint32_t kFmt = FP8 ? 0u : 1u;  // e4m3 / bf16
     constexpr uint32_t idesc_qk = umma_idesc(kFmt, kFmt, 0, 0, 128, 128);
     constexpr uint32_t idesc_pv = umma_idesc(kFmt, kFmt, 0, 1, 128, 128);
-    uint32_t kv_cnt = 0, q_cnt = 0;
-    uint32_t p_cnt[2] = {0, 0};
+    uint32_t ring_base = 0, q_cnt = 0, p_cnt = 0;
     bool ok = true;
     // descriptors are built once; a byte offset b inside a tile is an addition of b >> 4 to the low word
     const uint64_t q_desc = umma_desc_sw128(smem_u32(sQ), 0, 1024);
@@ -309,15 +311,15 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (!ok) break;
       PT_MARK(1)
       ++q_cnt;
-      tc_fence_after();
+      // ring positions in the producer's order K0, K1, V0, K2, V1, ..., K(n-1), V(n-2), V(n-1)
+      auto pos_k = [&](int j) { return ring_base + (uint32_t)(j == 0 ? 0 : 2 * j - 1); };
+      auto pos_v = [&](int j) { return ring_base + (uint32_t)(j == n_it - 1 ? 2 * n_it - 1 : 2 * j + 2); };
 
       auto issue_qk = [&](int i) -> bool {
-        const uint32_t stage = kv_cnt % NS;
-        const uint32_t ph = (kv_cnt / NS) & 1;
+        const uint32_t pos = pos_k(i), stage = pos % NS;
         PT_MARK(0)
-        if (!mbar_wait(BAR(kKvFull + stage), ph, wctx, 201)) return false;
+        if (!mbar_wait(BAR(kKvFull + stage), (pos / NS) & 1, wctx, 201)) return false;
         PT_MARK(2)
-        tc_fence_after();
         if (lane == 0) {
           const uint64_t kd = k_desc0 + (uint64_t)stage * (Cfg::kTileBytes >> 4);
 #pragma unroll
@@ -325,32 +327,27 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             // 32 bytes of K extent per step inside a 128-byte swizzled row; bf16 tiles continue in
             // the second slab after four steps.
             const uint64_t off = FP8 ? (uint64_t)(k * 2) : (uint64_t)((k >> 2) * (Cfg::kSlabBytes >> 4) + (k & 3) * 2);
-            if (FP8) umma_f8_ss(tS[i & 1], q_desc + off, kd + off, idesc_qk, k > 0);
-            else umma_f16_ss(tS[i & 1], q_desc + off, kd + off, idesc_qk, k > 0);
+            if (FP8) umma_f8_ss(tS[s], q_desc + off, kd + off, idesc_qk, k > 0);
+            else umma_f16_ss(tS[s], q_desc + off, kd + off, idesc_qk, k > 0);
           }
+          umma_commit(BAR(kSFull + s));
           umma_commit(BAR(kKvEmpty + stage));
-          umma_commit(BAR(kSFull + (i & 1)));
-          if (i == n_it - 1) umma_commit(BAR(kQEmpty));
         }
         __syncwarp();
-        ++kv_cnt;
         return true;
       };
       auto issue_pv = [&](int i) -> bool {
-        const int s = i & 1;
-        const uint32_t stage = kv_cnt % NS;
-        const uint32_t ph = (kv_cnt / NS) & 1;
+        const uint32_t pos = pos_v(i), stage = pos % NS;
         PT_MARK(0)
-        if (!mbar_wait(BAR(kKvFull + stage), ph, wctx, 202)) return false;
+        if (!mbar_wait(BAR(kKvFull + stage), (pos / NS) & 1, wctx, 202)) return false;
         PT_MARK(3)
-        if (!mbar_wait(BAR(kPFull + s), p_cnt[s] & 1, wctx, 203)) return false;
+        if (!mbar_wait(BAR(kPHalf + s), p_cnt & 1, wctx, 203)) return false;  // first half of P_s
         PT_MARK(4)
-        ++p_cnt[s];
         tc_fence_after();
-        if (lane == 0) {
-          const uint64_t vd = v_desc0 + (uint64_t)stage * (Cfg::kTileBytes >> 4);
+        const uint64_t vd = v_desc0 + (uint64_t)stage * (Cfg::kTileBytes >> 4);
+        auto pv_steps = [&](int k0, int k1) {
 #pragma unroll
-          for (int k = 0; k < Cfg::kKSteps; ++k) {
+          for (int k = k0; k < k1; ++k) {
             // V is MN-major: one k step = kMmaK token rows of 128 B; the second 64-channel slab of a
             // bf16 tile is reached through the leading byte offset.
             const uint64_t db = vd + (uint64_t)(k * ((Cfg::kMmaK * 128) >> 4));
@@ -358,24 +355,49 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if (FP8) umma_f8_ts(tO[s], a_t, db, idesc_pv, (i >= 2) || (k > 0));
             else umma_f16_ts(tO[s], a_t, db, idesc_pv, (i >= 2) || (k > 0));
           }
+        };
+        if (lane == 0) pv_steps(0, Cfg::kKSteps / 2);
+        __syncwarp();
+        PT_MARK(0)
+        if (!mbar_wait(BAR(kPFull + s), p_cnt & 1, wctx, 204)) return false;  // second half
+        PT_MARK(4)
+        ++p_cnt;
+        tc_fence_after();
+        if (lane == 0) {
+          pv_steps(Cfg::kKSteps / 2, Cfg::kKSteps);
           umma_commit(BAR(kKvEmpty + stage));
         }
         __syncwarp();
-        ++kv_cnt;
         return true;
       };
 
-      ok = issue_qk(0);
-      if (ok && n_it > 1) ok = issue_qk(1);
-      for (int i = 0; i < n_it && ok; ++i) {
+      if (s < n_it) ok = issue_qk(s);
+      int last_qk = (s < n_it) ? s : -1;
+      for (int i = s; i < n_it && ok; i += 2) {
         ok = issue_pv(i);
-        if (ok && i + 2 < n_it) ok = issue_qk(i + 2);
+        if (ok && i + 2 < n_it) {
+          ok = issue_qk(i + 2);
+          last_qk = i + 2;
+        }
       }
-      if (ok && lane == 0) umma_commit(BAR(kOFinal));
+      if (!ok) break;
+      (void)last_qk;
+      // Q is free once the QK MMAs of BOTH streams have completed, O is final once both streams' PV
+      // MMAs have: each issuer signals for its own MMAs (a stream without work arrives directly)
+      if (lane == 0) {
+        if (s < n_it) {
+          umma_commit(BAR(kQEmpty));
+          umma_commit(BAR(kOFinal));
+        } else {
+          mbar_arrive(BAR(kQEmpty));
+          mbar_arrive(BAR(kOFinal));
+        }
+      }
       __syncwarp();
+      ring_base += 2 * (uint32_t)n_it;
     }
     PT_MARK(0)
-    PT_FLUSH(32)
+    if (s == 0) { PT_FLUSH(32) } else { PT_FLUSH(40) }
   } else if (warp < 8) {
     // ===================================== softmax + epilogue ===================================
     setmaxnreg_inc<216>();
@@ -450,6 +472,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (!row_active) {
           // idle half of a 64-row tile: only the barrier protocol
           tc_fence_before();
+          mbar_arrive(BAR(kPHalf + grp));
           mbar_arrive(BAR(kPFull + grp));
           continue;
         }
@@ -498,37 +521,25 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             bm = fmaxf(m0, m1) * p.scale_log2;
           }
         } else {
-          // common case: the 32-column chunks arrive while the maximum of the previous one is taken
+          // common case: two 64-column halves; the second arrives while the maximum of the first is taken
           float m0, m1;
           tmem_ld32(t_row + 0, su + 0);
-          tmem_wait_ld();
           tmem_ld32(t_row + 32, su + 32);
+          tmem_wait_ld();
+          tmem_ld32(t_row + 64, su + 64);
+          tmem_ld32(t_row + 96, su + 96);
           m0 = fmax3(sv[0], sv[1], sv[2]);
           m1 = fmax3(sv[3], sv[4], sv[5]);
 #pragma unroll
-          for (int c = 6; c < 30; c += 4) {
+          for (int c = 6; c < 62; c += 4) {
             m0 = fmax3(m0, sv[c], sv[c + 1]);
             m1 = fmax3(m1, sv[c + 2], sv[c + 3]);
           }
-          m0 = fmax3(m0, sv[30], sv[31]);
-          tmem_wait_ld();
-          tmem_ld32(t_row + 64, su + 64);
-#pragma unroll
-          for (int c = 32; c < 64; c += 4) {
-            m0 = fmax3(m0, sv[c], sv[c + 1]);
-            m1 = fmax3(m1, sv[c + 2], sv[c + 3]);
-          }
-          tmem_wait_ld();
-          tmem_ld32(t_row + 96, su + 96);
-#pragma unroll
-          for (int c = 64; c < 96; c += 4) {
-            m0 = fmax3(m0, sv[c], sv[c + 1]);
-            m1 = fmax3(m1, sv[c + 2], sv[c + 3]);
-          }
+          m0 = fmax3(m0, sv[62], sv[63]);
           tmem_wait_ld();
           PT_MARK(2)
 #pragma unroll
-          for (int c = 96; c < 128; c += 4) {
+          for (int c = 64; c < 128; c += 4) {
             m0 = fmax3(m0, sv[c], sv[c + 1]);
             m1 = fmax3(m1, sv[c + 2], sv[c + 3]);
           }
@@ -593,11 +604,25 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               const int c = c4 * 32 + e * 2;
               float x0, x1;
               unpack2(ffma2(pack2(sv[c], sv[c + 1]), sc2, nm2), x0, x1);
-              x0 = ex2_approx(x0);
-              x1 = ex2_approx(x1);
-              if (e & 1) s1 = fadd2(s1, pack2(x0, x1));
-              else s0 = fadd2(s0, pack2(x0, x1));
+              uint64_t pe;
+              if ((e & 7) < BSA_EX2_EMU8) {
+                pe = ex2_emu2(x0, x1);
+                unpack2(pe, x0, x1);
+              } else {
+                x0 = ex2_approx(x0);
+                x1 = ex2_approx(x1);
+                pe = pack2(x0, x1);
+              }
+              if (e & 1) s1 = fadd2(s1, pe);
+              else s0 = fadd2(s0, pe);
               pk[e] = pack_bf16x2(x0, x1);
+            }
+            if (c4 == 2) {
+              // the first half of P_s (four MMA k steps) is released on its own barrier; waiting for its
+              // stores only now, after the third chunk's arithmetic, keeps their latency off the path
+              tmem_wait_st();
+              tc_fence_before();
+              mbar_arrive(BAR(kPHalf + grp));
             }
             tmem_st16(tS[grp] + lane_base + c4 * 16, pk);
           }
@@ -610,6 +635,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         PT_MARK(4)
         tmem_wait_st();
         tc_fence_before();
+        if (FP8) mbar_arrive(BAR(kPHalf + grp));
         mbar_arrive(BAR(kPFull + grp));
         PT_MARK(5)
       }
