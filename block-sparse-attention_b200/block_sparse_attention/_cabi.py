@@ -118,6 +118,7 @@ SIGNATURES = {
                                        ctypes.POINTER(ctypes.c_int64), _vp]),
     "bsa_quantize_sage": (ctypes.c_int, [_vp] * 11 + [_i32] * 4 + [_vp]),
     "bsa_quantize_sage_scratch_floats": (ctypes.c_int64, [_i32, _i32, _i32]),
+    "bsa_quantize_sage_static": (ctypes.c_int, [_vp] * 9 + [_i32] * 4 + [_vp]),
     "bsa_mask_to_q2k": (ctypes.c_int, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp]),
     "bsa_q2k_to_k2q": (ctypes.c_int, [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
     "bsa_build_k2q_csr": (ctypes.c_int, [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),

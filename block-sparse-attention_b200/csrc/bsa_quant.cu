@@ -241,3 +241,51 @@ extern "C" int bsa_quantize_sage(const void* q, const void* k, const void* v, vo
   if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "quantiser launch: %s", cudaGetErrorString(e));
   return BSA_OK;
 }
+
+// -------------------------------------------------------------------------------------------------
+// Quantiser entry point that owns its scratch (no counterpart in the reference).
+//
+// Some hosts of this library have no way to hand over scratch memory: an inference server that froze
+// its memory pool after start-up, a C or Rust service that links the library without any tensor
+// allocator, a latency-critical loop where a cudaMalloc would stall the whole device.  For them the
+// K-mean vector and the per-chunk statistics live in the fixed device array below instead of in
+// caller-provided buffers.  The array is part of the library image: every GPU that loads the library
+// holds these 4 MiB until the process exits.
+// -------------------------------------------------------------------------------------------------
+namespace bsa {
+constexpr long long kStaticScratchFloats = BSA_QUANTIZE_STATIC_SCRATCH_FLOATS;  // 4 MiB
+static __device__ __align__(256) float g_quant_scratch[kStaticScratchFloats];
+}  // namespace bsa
+
+extern "C" int bsa_quantize_sage_static(const void* q, const void* k, const void* v, void* q8, void* k8, void* v8,
+                                        float* q_scale, float* k_scale, float* v_scale, int32_t B, int32_t H,
+                                        int32_t Sq, int32_t Sk, void* cuda_stream) {
+  if (B < 1 || H < 1 || Sq < 1 || Sk < 1)
+    return set_error(BSA_ERR_INVALID, "bsa_quantize_sage_static: non-positive extent");
+  const long long mean_floats = (long long)B * H * 128;
+  const long long need = mean_floats + bsa_quantize_sage_scratch_floats(B, H, Sk);
+  if (need > kStaticScratchFloats)
+    return set_error(BSA_ERR_WORKSPACE,
+                     "bsa_quantize_sage_static: B*H*(1 + 2*ceil(Sk/1024))*128 = %lld floats exceed the built-in "
+                     "scratch of %lld floats; use bsa_quantize_sage with caller-provided scratch",
+                     need, kStaticScratchFloats);
+  // In host code the array's name is only a handle; the device address has to be asked for, once per
+  // device, with that device current.  This first call per device is the set-up.
+  static float* scratch_of_device[64] = {nullptr};
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
+    return set_error(BSA_ERR_CUDA, "bsa_quantize_sage_static: cannot identify the current device");
+  float* scratch = scratch_of_device[dev];
+  if (scratch == nullptr) {
+    void* addr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&addr, g_quant_scratch);
+    if (e != cudaSuccess || addr == nullptr)
+      return set_error(BSA_ERR_CUDA, "bsa_quantize_sage_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+    scratch = static_cast<float*>(addr);
+    scratch_of_device[dev] = scratch;
+  }
+  // Every slot that is read has been written earlier in the same call (statistics kernel -> finish kernel
+  // -> apply kernel), so nothing has to be cleared between calls.
+  return bsa_quantize_sage(q, k, v, q8, k8, v8, q_scale, k_scale, v_scale, /*k_mean=*/scratch,
+                           /*partials=*/scratch + mean_floats, B, H, Sq, Sk, cuda_stream);
+}

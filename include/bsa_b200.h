@@ -128,6 +128,25 @@ int bsa_quantize_sage(const void* q, const void* k, const void* v, void* q8, voi
 int64_t bsa_quantize_sage_scratch_floats(int32_t B, int32_t H, int32_t Sk);
 
 /*
+ * Same quantiser for callers that cannot provide scratch memory (this entry point has no counterpart in
+ * the reference).  Think of a server whose memory pool is frozen after start-up, or a plain C host
+ * without a device allocator of its own: the K mean and the chunk statistics are kept in a 4 MiB array
+ * that is part of the library image (each GPU that loads the library holds it until the process ends).
+ * Nothing is allocated or freed, here or in anything it calls.
+ *   limit   : B*H*(1 + 2*ceil(Sk/1024))*128 floats <= BSA_QUANTIZE_STATIC_SCRATCH_FLOATS (1 Mi);
+ *             larger problems are rejected with BSA_ERR_WORKSPACE and must use bsa_quantize_sage.
+ *   set-up  : the first call on each device looks the array's device address up; make that first call
+ *             outside any stream capture.
+ *   sharing : all calls on a device use the same array.  Calls that can overlap on the GPU (different
+ *             streams without ordering) race on it; serialise them.  No state has to be cleared between
+ *             calls: every value read is written earlier in the same call.
+ */
+#define BSA_QUANTIZE_STATIC_SCRATCH_FLOATS (1 << 20)
+int bsa_quantize_sage_static(const void* q, const void* k, const void* v, void* q8, void* k8, void* v8,
+                             float* q_scale, float* k_scale, float* v_scale, int32_t B, int32_t H, int32_t Sq,
+                             int32_t Sk, void* cuda_stream);
+
+/*
  * Block mask -> q2k index.  mask [B,H,Nq,Nkv] uint8 (non-zero = attend).  Writes the attended KV block
  * ids of every row in ascending order to index [B,H,Nq,cap] (entries beyond the count are set to 0)
  * and the count to nums [B,H,Nq]; counts above cap are clamped.
