@@ -111,13 +111,13 @@ def _extent(sizes, b, h, j):
 
 
 def attention_gathered(q, k, v, index, count, nums=None, sizes=None, scale=None, blk=128, heads=None,
-                       batches=None, return_lse=True):
+                       batches=None, return_lse=True, tiles=None):
     """FP32 attention over exactly the selected valid KV tokens of every query block (MHA or unpacked GQA).
 
     Restates tests/test_bsa_fp8_blk128.py:45-77 (``sparse_reference``: live prefix of the index row,
     tokens < Sk, optional rank-1/2/3 block extents, empty rows -> 0) and
     tests/test_flash_fwd.py:473-523 (``_reference_variable_case``, which also yields the LSE, -inf for
-    empty rows).  ``heads`` / ``batches`` restrict the computation to a subset (used for big configs)."""
+    empty rows).  ``heads`` / ``batches`` / ``tiles`` restrict the computation to a subset (big configs)."""
     B, Hq, Sq, D = q.shape
     Hkv, Sk = k.shape[1], k.shape[2]
     G = Hq // Hkv
@@ -130,7 +130,7 @@ def attention_gathered(q, k, v, index, count, nums=None, sizes=None, scale=None,
         for h in (range(Hq) if heads is None else heads):
             hk = h // G
             kf, vf = k[b, hk].float(), v[b, hk].float()
-            for m in range(Nq):
+            for m in (range(Nq) if tiles is None else tiles):
                 n = count if nums is None else int(nums[b, h, m])
                 n = max(0, min(n, index.shape[-1]))
                 s, e = m * blk, min((m + 1) * blk, Sq)
@@ -154,7 +154,8 @@ def attention_gathered(q, k, v, index, count, nums=None, sizes=None, scale=None,
     return (out, lse) if return_lse else out
 
 
-def attention_gathered_packed(q, k, v, index, count, nums=None, sizes=None, scale=None, blk=128, kv_heads=None):
+def attention_gathered_packed(q, k, v, index, count, nums=None, sizes=None, scale=None, blk=128, kv_heads=None,
+                              tiles=None):
     """Packed-GQA variant: ``index``/``nums`` are per (batch, kv head, packed tile); packed row r of a kv
     head is (seq = r // G, query head = hkv*G + r % G) (csrc/utils/pack_gqa.py:10-35,
     tests/test_flash_fwd.py:189-215, :273-274)."""
@@ -171,7 +172,7 @@ def attention_gathered_packed(q, k, v, index, count, nums=None, sizes=None, scal
             kf, vf = k[b, hk].float(), v[b, hk].float()
             # packed query matrix [Sq*G, D]
             qp = q[b, hk * G:(hk + 1) * G].float().permute(1, 0, 2).reshape(Sq * G, D)
-            for m in range(Nt):
+            for m in (range(Nt) if tiles is None else tiles):
                 n = count if nums is None else int(nums[b, hk, m])
                 n = max(0, min(n, index.shape[-1]))
                 s, e = m * blk, min((m + 1) * blk, Sq * G)
