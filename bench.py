@@ -37,6 +37,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(ROOT, "block-sparse-attention_b200"))
 sys.path.insert(0, ROOT)
 
+EXTRA_WORKLOADS = ("cfg3", "cfg4", "cfg5")  # forward-only lines for the other BASELINE configs
+
 WORKLOADS = {
     # name: (B per GPU, H, S, blocks per row)
     "cfg2": (2, 32, 32768, 26),
@@ -169,13 +171,112 @@ def run_reference(args, rank, world):
     print(json.dumps(line), flush=True)
 
 
+def _time_cuda(fn, warmup, steps):
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(steps)]
+    for a, b in evs:
+        a.record()
+        fn()
+        b.record()
+    torch.cuda.synchronize()
+    return statistics.median(a.elapsed_time(b) for a, b in evs)
+
+
+def run_extra(args):
+    """Forward-only measurements of BASELINE configs 3, 4 and 5 on one GPU (inputs resident in HBM).
+    cfg4 also times the Sage quantiser and the split-KV combine against the HBM roofline."""
+    from block_sparse_attention import (bsa_attn_fwd, bsa_fp8_blk128_fwd, check_device_status,
+                                        quantize_sage_bhsd)
+    from oracle import workloads
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    peaks, peak_kind = load_peaks()
+    bf16_peak = float(peaks.get("bf16_tflops", 1590.0))
+    hbm_peak = float(peaks.get("hbm_gbs", 6650.0))
+
+    def rnd(shape, seed):
+        g = torch.Generator(device=dev).manual_seed(seed)
+        return torch.randn(shape, generator=g, device=dev).to(torch.bfloat16)
+
+    line = {"metric": "sparse_effective_tflops_fwd", "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps,
+            "warmup": args.warmup, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "data": "synthetic", "peak_source": peak_kind}
+    if args.workload == "cfg3":
+        index, nums = workloads.config3_metadata(seed=0)
+        q, k, v = rnd((1, 64, 65536, D), 1), rnd((1, 8, 65536, D), 2), rnd((1, 8, 65536, D), 3)
+        ic, nc = index.to(dev), nums.to(dev)
+        out = torch.empty_like(q)
+        ms = _time_cuda(lambda: bsa_attn_fwd(q, k, v, ic, 0, q2k_block_nums=nc, pack_gqa=True, out=out,
+                                             sparse_block_size=128), args.warmup, args.steps)
+        pairs = int(nums.sum())
+        tf = 4.0 * pairs * 128 * 128 * D / (ms * 1e-3) / 1e12
+        line.update({"value": tf, "ms_per_step": ms, "dtype": "bf16",
+                     "config": {"workload": "cfg3: BF16 GQA blk128 forward, B=1 Hq=64 Hkv=8 pack_gqa S=65536, "
+                                            "Poisson(25) blocks per packed tile, 2% empty", "pairs": pairs},
+                     "roofline": {"bound": "tensor", "achieved": tf, "peak": bf16_peak, "unit": "TFLOP/s",
+                                  "frac": tf / bf16_peak, "frac_of_nominal_2250": tf / 2250.0, "traffic": None}})
+    elif args.workload == "cfg5":
+        index, nums = workloads.config5_metadata(seed=0)
+        q, k, v = (rnd((4, 16, 16384, D), s) for s in (1, 2, 3))
+        ic, nc = index.to(dev), nums.to(dev)
+        out = torch.empty_like(q)
+        ms = _time_cuda(lambda: bsa_attn_fwd(q, k, v, ic, 0, q2k_block_nums=nc, out=out, sparse_block_size=64,
+                                             kv_splits="auto"), args.warmup, args.steps)
+        pairs = int(nums.sum())
+        tf = 4.0 * pairs * 64 * 64 * D / (ms * 1e-3) / 1e12
+        # compulsory bytes: Q + O once, every active pair's K and V block through L2 (upper bound), LSE, index rows
+        comp = 2 * q.numel() * 2 + pairs * 64 * 2 * D * 2 + 4 * 16 * 16384 * 4 + pairs * 4
+        gbs = comp / (ms * 1e-3) / 1e9
+        line.update({"value": tf, "ms_per_step": ms, "dtype": "bf16",
+                     "config": {"workload": "cfg5: BF16 MHA blk64 forward, B=4 H=16 S=16384, 1% rows x 256 blocks, "
+                                            "others 2-8, kv_splits=auto", "pairs": pairs},
+                     "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm_peak, "unit": "GB/s",
+                                  "frac": gbs / hbm_peak, "traffic": None,
+                                  "note": "compulsory bytes with every active pair's K/V counted once"},
+                     "tensor_frac_of_measured": tf / bf16_peak})
+    else:  # cfg4
+        H, S = 24, 76800
+        index, nums = workloads.config4_metadata(seed=0)
+        q = rnd((1, H, S, D), 1)
+        k = workloads.k_with_channel_bias((1, H, S, D), 2, dev)
+        v = rnd((1, H, S, D), 3)
+        ic, nc = index.to(dev), nums.to(dev)
+        ms_quant = _time_cuda(lambda: quantize_sage_bhsd(q, k, v), args.warmup, args.steps)
+        quant = quantize_sage_bhsd(q, k, v)
+        ms4 = _time_cuda(lambda: bsa_fp8_blk128_fwd(*quant, ic, 0, q2k_block_nums=nc, kv_splits=4),
+                         args.warmup, args.steps)
+        ms1 = _time_cuda(lambda: bsa_fp8_blk128_fwd(*quant, ic, 0, q2k_block_nums=nc, kv_splits=1),
+                         args.warmup, args.steps)
+        pairs = int(nums.sum())
+        flops = 4.0 * pairs * 128 * 128 * D
+        tf4, tf1 = flops / (ms4 * 1e-3) / 1e12, flops / (ms1 * 1e-3) / 1e12
+        fp8_peak = 2.0 * bf16_peak  # no FP8 GEMM peak is measured: twice the measured BF16 figure (assumption)
+        n = q.numel()
+        quant_bytes = 3 * n + 5 * n + 5 * n
+        line.update({"value": tf4, "ms_per_step": ms4, "dtype": "e4m3",
+                     "config": {"workload": "cfg4: Sage FP8 blk128 forward, B=1 H=24 S=76800, band 30 + 60 far blocks "
+                                            "(19.9% density), kv_splits=4 incl. combine", "pairs": pairs},
+                     "unsplit_ms": ms1, "unsplit_tflops": tf1,
+                     "roofline": {"bound": "tensor", "achieved": tf4, "peak": fp8_peak, "unit": "TFLOP/s",
+                                  "frac": tf4 / fp8_peak, "frac_of_nominal_4500": tf4 / 4500.0, "traffic": None,
+                                  "note": "FP8 peak taken as 2x the measured BF16 GEMM peak"},
+                     "quantiser": {"ms": ms_quant, "bound": "hbm", "achieved": quant_bytes / (ms_quant * 1e-3) / 1e9,
+                                   "peak": hbm_peak, "unit": "GB/s",
+                                   "frac": quant_bytes / (ms_quant * 1e-3) / 1e9 / hbm_peak,
+                                   "bytes": "3|Q| + 5|K| + 5|V|"}})
+    check_device_status()
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="cfg2", choices=sorted(WORKLOADS) + list(EXTRA_WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--fwd-only", action="store_true", help="profiling aid: skip the backward pass")
@@ -186,6 +287,10 @@ def main():
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
 
+    if args.workload in EXTRA_WORKLOADS:
+        if rank == 0:
+            run_extra(args)
+        return
     if args.impl == "reference":
         run_reference(args, rank, world)
         return
