@@ -88,6 +88,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// Same test, but the hardware may keep the thread suspended for up to `hint_ns` until the phase
+// completes, instead of returning early: a waiting warp then issues (almost) no instructions.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok != 0;
+}
 
 // Shared abort flag + global status buffer handed to every bounded wait.
 struct WaitCtx {
@@ -103,24 +116,22 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   bool done = mbar_try_wait(bar, parity);
   if (!done) {
     const uint64_t t0 = globaltimer_ns();
-    uint32_t it = 0;
     for (;;) {
-      if (mbar_try_wait(bar, parity)) {
+      // suspended in hardware for up to 0.1 ms per attempt: no busy spinning next to the working warps
+      if (mbar_try_wait_suspend(bar, parity, 100000u)) {
         done = true;
         break;
       }
-      if ((++it & 0xffu) == 0) {
-        if (*ctx.abort_flag) break;
-        if (globaltimer_ns() - t0 > BSA_WAIT_LIMIT_NS) {
-          *ctx.abort_flag = 1;
-          if (atomicCAS(ctx.status, 0, (int)kStatusWaitTimeout) == 0) {
-            ctx.status[1] = (int)blockIdx.x;
-            ctx.status[2] = site;
-            ctx.status[3] = (int)threadIdx.x;
-          }
-          __threadfence();
-          break;
+      if (*ctx.abort_flag) break;
+      if (globaltimer_ns() - t0 > BSA_WAIT_LIMIT_NS) {
+        *ctx.abort_flag = 1;
+        if (atomicCAS(ctx.status, 0, (int)kStatusWaitTimeout) == 0) {
+          ctx.status[1] = (int)blockIdx.x;
+          ctx.status[2] = site;
+          ctx.status[3] = (int)threadIdx.x;
         }
+        __threadfence();
+        break;
       }
     }
   }
