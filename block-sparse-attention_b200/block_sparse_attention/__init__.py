@@ -14,6 +14,8 @@ _EXPORTS = {
     "block_mask_to_q2k": ".bsa_attn_interface",
     "check_device_status": ".bsa_attn_interface",
     "quantize_sage_bhsd": ".bsa_fp8_quant",
+    "block_sparse_attention": ".autograd",
+    "BlockSparseAttentionFunction": ".autograd",
 }
 
 __all__ = sorted(_EXPORTS)

@@ -39,6 +39,7 @@ class FwdArgs(ctypes.Structure):
         ("v_scale", ctypes.c_void_p),
         ("partial_o", ctypes.c_void_p),
         ("partial_lse", ctypes.c_void_p),
+        ("work_order", ctypes.c_void_p),
         ("status", ctypes.c_void_p),
         ("q_stride", _c_i64x3),
         ("k_stride", _c_i64x3),
@@ -121,6 +122,8 @@ SIGNATURES = {
     "bsa_quantize_sage_static": (ctypes.c_int, [_vp] * 9 + [_i32] * 4 + [_vp]),
     "bsa_mask_to_q2k": (ctypes.c_int, [_vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32, _vp]),
     "bsa_q2k_to_k2q": (ctypes.c_int, [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "bsa_lpt_order": (ctypes.c_int, [_vp, _i32, _i32, _vp, _vp, _vp]),
+    "bsa_lpt_order_scratch_ints": (ctypes.c_int64, [_i32, _i32]),
     "bsa_build_k2q_csr": (ctypes.c_int, [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
     "bsa_bwd": (ctypes.c_int, [ctypes.POINTER(BwdArgs), _vp]),
     "bsa_bwd_workspace_bytes": (ctypes.c_int64, [_i32, _i32, _i32, _i32, _i32]),

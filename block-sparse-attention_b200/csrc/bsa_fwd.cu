@@ -35,6 +35,7 @@ struct FwdParams {
   const int32_t* __restrict__ q2k_index;
   const int32_t* __restrict__ q2k_nums;
   const int32_t* __restrict__ block_sizes;
+  const int32_t* __restrict__ work_order;
   const float* __restrict__ q_scale;
   const float* __restrict__ k_scale;
   const float* __restrict__ v_scale;
@@ -71,6 +72,9 @@ struct FwdCfg {
   static constexpr int kSlabs = FP8 ? 1 : 2;           // 128-byte-wide column slabs per tile
   static constexpr int kSlabBytes = 128 * 128;         // 128 rows x 128 B
   static constexpr int kStages = FP8 ? 8 : 5;
+  // each stream owns a private ring of K/V stages (stream 0 the first kRing0 stages), consumed strictly in
+  // order by that stream's issuing warp: a parity wait is then never more than one phase behind
+  static constexpr int kRing0 = FP8 ? 4 : 3;
   static constexpr int kOBytes = 128 * 128 * 2;  // bf16 output staging
   static constexpr int kMmaK = FP8 ? 32 : 16;
   static constexpr int kKSteps = 128 / kMmaK;
@@ -92,6 +96,13 @@ __device__ __forceinline__ WorkItem decode_work(const FwdParams& p, int w) {
   WorkItem t;
   t.split = w % p.splits;
   int r = w / p.splits;
+  if (p.work_order) {
+    r = p.work_order[r];
+    if (r < 0 || r >= p.B * p.Hidx * p.NqT) {  // a corrupt order must not turn into a wild access
+      if (atomicCAS(p.status, 0, (int)kStatusBadIndex) == 0) p.status[2] = r;
+      r = 0;
+    }
+  }
   t.m = r % p.NqT;
   r /= p.NqT;
   t.hidx = r % p.Hidx;
@@ -147,7 +158,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const uint32_t bar_base = smem_u32(bars);
   auto BAR = [&](int i) { return bar_base + (uint32_t)i * 8u; };
   constexpr int kQFull = 0, kQEmpty = 1, kKvFull = 2, kKvEmpty = 2 + NS, kSFull = 2 + 2 * NS,
-                kPFull = kSFull + 2, kOFinal = kPFull + 2, kEpiA = kOFinal + 1, kEpiB = kEpiA + 1,
+                kPFull = kSFull + 2, kOFinal = kPFull + 2, kEpiA = kOFinal + 2, kEpiB = kEpiA + 1,
                 kGrpA = kEpiB + 1, kGrpB = kGrpA + 2, kPHalf = kGrpB + 2, kNumBars = kPHalf + 2;
   float2 (*s_stats)[128] = reinterpret_cast<float2 (*)[128]>(bars + 32);  // [2][128] (max, sum)
   uint32_t& s_tmem_base = *reinterpret_cast<uint32_t*>(bars + 32 + 256);
@@ -175,7 +186,8 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       mbar_init(BAR(kPFull + s), 128);
       mbar_init(BAR(kPHalf + s), 128);
     }
-    mbar_init(BAR(kOFinal), 2);
+    mbar_init(BAR(kOFinal), 1);  // one per stream: a stream without work in a tile neither arrives nor is waited for
+    mbar_init(BAR(kOFinal + 1), 1);
     mbar_init(BAR(kEpiA), kSoftmaxThreads);
     mbar_init(BAR(kEpiB), kSoftmaxThreads);
     for (int s = 0; s < 2; ++s) {
@@ -208,7 +220,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   if (warp == kLoadWarp) {
     // ======================================= TMA producer =======================================
     setmaxnreg_dec<56>();
-    uint32_t kv_cnt = 0;  // stages produced so far
+    uint32_t ring_cnt[2] = {0, 0};  // tiles produced so far into each stream's ring
     uint32_t q_cnt = 0;
     bool ok = true;
     PT_DECL
@@ -233,9 +245,10 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       ++q_cnt;
 
       // K/V tiles in MMA consumption order: K0, K1, V0, K2, V1, ..., K(n-1), V(n-2), V(n-1)
-      auto issue_tile = [&](const CUtensorMap* tm, int blk0, int blk1) -> bool {
-        const uint32_t stage = kv_cnt % NS;
-        const uint32_t ph = (kv_cnt / NS) & 1;
+      auto issue_tile = [&](const CUtensorMap* tm, int strm, int blk0, int blk1) -> bool {
+        const uint32_t depth = strm ? (uint32_t)(NS - Cfg::kRing0) : (uint32_t)Cfg::kRing0;
+        const uint32_t stage = (strm ? (uint32_t)Cfg::kRing0 : 0u) + ring_cnt[strm] % depth;
+        const uint32_t ph = (ring_cnt[strm] / depth) & 1;
         PT_MARK(0)
         if (!mbar_wait(BAR(kKvEmpty + stage), ph ^ 1, wctx, 101)) return false;
         PT_MARK(2)
@@ -256,7 +269,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             }
           }
         }
-        ++kv_cnt;
+        ++ring_cnt[strm];
         return true;
       };
       // block ids of KV iteration `it` (relative to the row start)
@@ -271,14 +284,14 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       };
       int j0, j1, pj0, pj1;
       fetch(t.it_begin, pj0, pj1);
-      ok = issue_tile(&tm_k, pj0, pj1);
+      ok = issue_tile(&tm_k, 0, pj0, pj1);
       for (int i = 0; i < n_it && ok; ++i) {
         if (i + 1 < n_it) {
           fetch(t.it_begin + i + 1, j0, j1);
-          ok = issue_tile(&tm_k, j0, j1);
+          ok = issue_tile(&tm_k, (i + 1) & 1, j0, j1);
           if (!ok) break;
         }
-        ok = issue_tile(&tm_v, pj0, pj1);
+        ok = issue_tile(&tm_v, i & 1, pj0, pj1);
         pj0 = j0;
         pj1 = j1;
       }
@@ -295,7 +308,9 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     constexpr uint32_t kFmt = FP8 ? 0u : 1u;  // e4m3 / bf16
     constexpr uint32_t idesc_qk = umma_idesc(kFmt, kFmt, 0, 0, 128, 128);
     constexpr uint32_t idesc_pv = umma_idesc(kFmt, kFmt, 0, 1, 128, 128);
-    uint32_t ring_base = 0, q_cnt = 0, p_cnt = 0;
+    uint32_t ring_pos = 0, q_cnt = 0, p_cnt = 0;  // ring_pos: tiles of this stream's ring consumed so far
+    const uint32_t ring_depth = s ? (uint32_t)(NS - Cfg::kRing0) : (uint32_t)Cfg::kRing0;
+    const uint32_t ring_first = s ? (uint32_t)Cfg::kRing0 : 0u;
     bool ok = true;
     // descriptors are built once; a byte offset b inside a tile is an addition of b >> 4 to the low word
     const uint64_t q_desc = umma_desc_sw128(smem_u32(sQ), 0, 1024);
@@ -311,14 +326,12 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (!ok) break;
       PT_MARK(1)
       ++q_cnt;
-      // ring positions in the producer's order K0, K1, V0, K2, V1, ..., K(n-1), V(n-2), V(n-1)
-      auto pos_k = [&](int j) { return ring_base + (uint32_t)(j == 0 ? 0 : 2 * j - 1); };
-      auto pos_v = [&](int j) { return ring_base + (uint32_t)(j == n_it - 1 ? 2 * n_it - 1 : 2 * j + 2); };
-
+      // this stream's ring holds K(s), V(s), K(s+2), V(s+2), ... and is consumed in exactly that order
       auto issue_qk = [&](int i) -> bool {
-        const uint32_t pos = pos_k(i), stage = pos % NS;
+        const uint32_t stage = ring_first + ring_pos % ring_depth;
         PT_MARK(0)
-        if (!mbar_wait(BAR(kKvFull + stage), (pos / NS) & 1, wctx, 201)) return false;
+        if (!mbar_wait(BAR(kKvFull + stage), (ring_pos / ring_depth) & 1, wctx, 201)) return false;
+        ++ring_pos;
         PT_MARK(2)
         if (lane == 0) {
           const uint64_t kd = k_desc0 + (uint64_t)stage * (Cfg::kTileBytes >> 4);
@@ -337,9 +350,10 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         return true;
       };
       auto issue_pv = [&](int i) -> bool {
-        const uint32_t pos = pos_v(i), stage = pos % NS;
+        const uint32_t stage = ring_first + ring_pos % ring_depth;
         PT_MARK(0)
-        if (!mbar_wait(BAR(kKvFull + stage), (pos / NS) & 1, wctx, 202)) return false;
+        if (!mbar_wait(BAR(kKvFull + stage), (ring_pos / ring_depth) & 1, wctx, 202)) return false;
+        ++ring_pos;
         PT_MARK(3)
         if (!mbar_wait(BAR(kPHalf + s), p_cnt & 1, wctx, 203)) return false;  // first half of P_s
         PT_MARK(4)
@@ -382,19 +396,19 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
       if (!ok) break;
       (void)last_qk;
-      // Q is free once the QK MMAs of BOTH streams have completed, O is final once both streams' PV
-      // MMAs have: each issuer signals for its own MMAs (a stream without work arrives directly)
+      // Q is free once the QK MMAs of BOTH streams have completed: each issuer signals for its own MMAs
+      // (a stream without work arrives directly; it cannot arrive twice in one phase because the next Q
+      // tile, which it waits for first, is only loaded after this phase has completed).  O_s is final
+      // when stream s's own PV MMAs have completed.
       if (lane == 0) {
         if (s < n_it) {
           umma_commit(BAR(kQEmpty));
-          umma_commit(BAR(kOFinal));
+          umma_commit(BAR(kOFinal + s));
         } else {
           mbar_arrive(BAR(kQEmpty));
-          mbar_arrive(BAR(kOFinal));
         }
       }
       __syncwarp();
-      ring_base += 2 * (uint32_t)n_it;
     }
     PT_MARK(0)
     if (s == 0) { PT_FLUSH(32) } else { PT_FLUSH(40) }
@@ -405,7 +419,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const int row = threadIdx.x & 127;         // query row inside the tile = tensor-memory lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const bool row_active = (BLK == 128) || (row < 64);  // warp-uniform
-    uint32_t s_cnt = 0, of_cnt = 0, epi_a = 0, epi_b = 0, grp_a = 0, grp_b = 0;
+    uint32_t s_cnt = 0, of_cnt[2] = {0, 0}, epi_a = 0, epi_b = 0, grp_a = 0, grp_b = 0;
     bool ok = true;
     const bool need_mask_meta = (p.block_sizes != nullptr) || (p.Sk % BLK != 0);
     constexpr float kRescaleThreshold = FP8 ? 1.8073549f /* log2(448/128) */ : 8.0f;
@@ -644,9 +658,14 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       // ------------------------------------ tile epilogue ------------------------------------
       PT_MARK(0)
       if (n_it > 0) {
-        ok = mbar_wait(BAR(kOFinal), of_cnt & 1, wctx, 310 + grp);
+        ok = mbar_wait(BAR(kOFinal), of_cnt[0] & 1, wctx, 310 + grp);
         if (!ok) break;
-        ++of_cnt;
+        ++of_cnt[0];
+        if (n_it > 1) {
+          ok = mbar_wait(BAR(kOFinal + 1), of_cnt[1] & 1, wctx, 312 + grp);
+          if (!ok) break;
+          ++of_cnt[1];
+        }
         tc_fence_after();
       }
       PT_MARK(6)
@@ -815,6 +834,7 @@ extern "C" int bsa_fwd(const bsa_fwd_args* a, void* cuda_stream) {
   p.q2k_index = a->q2k_index;
   p.q2k_nums = a->q2k_nums;
   p.block_sizes = a->block_sizes;
+  p.work_order = a->work_order;
   p.q_scale = a->q_scale;
   p.k_scale = a->k_scale;
   p.v_scale = a->v_scale;

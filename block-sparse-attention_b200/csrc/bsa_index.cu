@@ -237,6 +237,75 @@ csr_sort_kernel(const int32_t* __restrict__ offsets, int32_t* __restrict__ indic
   }
 }
 
+// ------------------------------------------------------------------------------------------------
+// longest-first work order: stable counting sort of the rows by descending live count.
+//   hist layout: [(cap - count) * chunks + chunk], chunks of 1024 consecutive rows, so that one exclusive
+//   scan over the whole array yields, for every (count, chunk), the first output slot of that chunk's
+//   rows with that count.  Stability keeps rows of one (batch, head) adjacent inside a count class.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(1024)
+lpt_hist_kernel(const int32_t* __restrict__ nums, int rows, int cap, int chunks, int32_t* __restrict__ hist) {
+  const int chunk = blockIdx.x;
+  const int r = chunk * 1024 + threadIdx.x;
+  if (r < rows) {
+    const int c = max(0, min(nums[r], cap));
+    atomicAdd(hist + (long long)(cap - c) * chunks + chunk, 1);
+  }
+}
+
+__global__ void __launch_bounds__(1024)
+lpt_scan_kernel(int32_t* __restrict__ hist, long long total) {
+  __shared__ int warp_sums[32];
+  __shared__ int carry_s;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) carry_s = 0;
+  __syncthreads();
+  for (long long c0 = 0; c0 < total; c0 += 1024) {
+    const long long i = c0 + threadIdx.x;
+    const int v = (i < total) ? hist[i] : 0;
+    int x = v;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int y = __shfl_up_sync(0xffffffffu, x, o);
+      if (lane >= o) x += y;
+    }
+    if (lane == 31) warp_sums[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+      int w = warp_sums[lane];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, w, o);
+        if (lane >= o) w += y;
+      }
+      warp_sums[lane] = w;
+    }
+    __syncthreads();
+    const int carry = carry_s;
+    if (i < total) hist[i] = carry + (warp > 0 ? warp_sums[warp - 1] : 0) + x - v;
+    __syncthreads();
+    if (threadIdx.x == 1023) carry_s = carry + warp_sums[31];
+    __syncthreads();
+  }
+}
+
+__global__ void __launch_bounds__(1024)
+lpt_scatter_kernel(const int32_t* __restrict__ nums, int rows, int cap, int chunks, const int32_t* __restrict__ hist,
+                   int32_t* __restrict__ order) {
+  __shared__ int16_t s_cnt[1024];
+  const int chunk = blockIdx.x;
+  const int r = chunk * 1024 + threadIdx.x;
+  const int c = (r < rows) ? max(0, min(nums[r], cap)) : -1;
+  s_cnt[threadIdx.x] = (int16_t)c;
+  __syncthreads();
+  if (r < rows) {
+    int rank = 0;  // rows of this chunk with the same count and a smaller index
+    for (int j = 0; j < (int)threadIdx.x; ++j) rank += (s_cnt[j] == (int16_t)c);
+    const int pos = hist[(long long)(cap - c) * chunks + chunk] + rank;
+    if (pos >= 0 && pos < rows) order[pos] = r;
+  }
+}
+
 static int check_launch(const char* what) {
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "%s launch: %s", what, cudaGetErrorString(e));
@@ -315,4 +384,27 @@ extern "C" int bsa_build_k2q_csr(const int32_t* q2k_index, const int32_t* q2k_nu
     if ((rc = check_launch("csr_sort"))) return rc;
   }
   return BSA_OK;
+}
+
+extern "C" int64_t bsa_lpt_order_scratch_ints(int32_t rows, int32_t cap) {
+  if (rows < 1 || cap < 0) return 0;
+  return (int64_t)(cap + 1) * ((rows + 1023) / 1024);
+}
+
+extern "C" int bsa_lpt_order(const int32_t* q2k_nums, int32_t rows, int32_t cap, int32_t* order, int32_t* scratch,
+                             void* cuda_stream) {
+  if (!q2k_nums || !order || !scratch) return set_error(BSA_ERR_INVALID, "bsa_lpt_order: null pointer");
+  if (rows < 1 || cap < 0 || cap > 32000) return set_error(BSA_ERR_INVALID, "bsa_lpt_order: bad extent");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
+  const int chunks = (rows + 1023) / 1024;
+  const long long total = (long long)(cap + 1) * chunks;
+  cudaError_t e = cudaMemsetAsync(scratch, 0, sizeof(int32_t) * total, st);
+  if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "bsa_lpt_order memset: %s", cudaGetErrorString(e));
+  int rc;
+  lpt_hist_kernel<<<chunks, 1024, 0, st>>>(q2k_nums, rows, cap, chunks, scratch);
+  if ((rc = check_launch("lpt_hist"))) return rc;
+  lpt_scan_kernel<<<1, 1024, 0, st>>>(scratch, total);
+  if ((rc = check_launch("lpt_scan"))) return rc;
+  lpt_scatter_kernel<<<chunks, 1024, 0, st>>>(q2k_nums, rows, cap, chunks, scratch, order);
+  return check_launch("lpt_scatter");
 }

@@ -65,6 +65,9 @@ int bsa_num_sms(int device);
  * [splits, B, Hq, Sq, D] and its log-sum-exp to partial_lse [splits, B, Hq, Sq]; `out`/`lse` are not
  * touched and the caller runs bsa_fwd_combine afterwards.
  *
+ * work_order: the persistent CTAs walk the tile rows in this order (CTA c takes entries c, c+G, c+2G, ...
+ * of it, G = grid size).  NULL = natural order.
+ *
  * dtype = BSA_DTYPE_E4M3 selects the Sage FP8 path: q, k, v hold e4m3 bytes, q_scale [B,H,Sq],
  * k_scale [B,H,ceil(Sk/16)] and v_scale [H,D] are the multiplicative dequantisation factors
  * (contiguous f32), Hq must equal Hkv.
@@ -83,6 +86,7 @@ typedef struct bsa_fwd_args {
   const float* v_scale;
   float* partial_o;
   float* partial_lse;
+  const int32_t* work_order; /* NULL, or a permutation of the B*Hidx*Nq tile rows (see bsa_lpt_order) */
   int32_t* status;
   int64_t q_stride[3]; /* batch, head, seq */
   int64_t k_stride[3];
@@ -164,6 +168,16 @@ int bsa_mask_to_q2k(const uint8_t* mask, int32_t* index, int32_t* nums, int32_t 
 int bsa_q2k_to_k2q(const int32_t* q2k_index, const int32_t* q2k_nums, int32_t block_sparse_num,
                    int32_t B, int32_t H, int32_t Nq, int32_t cap, int32_t Nkv, int32_t* k2q_index,
                    int32_t* k2q_nums, void* cuda_stream);
+
+/*
+ * Longest-first work order for skewed per-row counts: order[0..rows) = the row ids sorted by descending
+ * clamp(q2k_nums[row], 0, cap), rows of equal count in ascending order (stable, deterministic).
+ * scratch: bsa_lpt_order_scratch_ints(rows, cap) int32.  The reference has no counterpart: it balances
+ * with the hardware work-stealing scheduler (csrc/utils/block_sparse_tile_scheduler.py:104-136).
+ */
+int bsa_lpt_order(const int32_t* q2k_nums, int32_t rows, int32_t cap, int32_t* order, int32_t* scratch,
+                  void* cuda_stream);
+int64_t bsa_lpt_order_scratch_ints(int32_t rows, int32_t cap);
 
 /*
  * Bucketed k2q CSR for the backward pass.  offsets [B,H,G,Nkv+1] (running per (b,h) across the G

@@ -140,3 +140,14 @@ def test_argument_errors():
         bsa_attn_bwd(x.half(), x.half(), x.half(), x.half(), x.half(), lse, idx, 1, sparse_block_size=128)
     with pytest.raises(AssertionError):
         bsa_attn_bwd(x, x, x[:, :1], x[:, :1], x, lse, idx, 1, sparse_block_size=128)  # GQA
+
+
+def test_autograd_function_matches_oracle_gradients():
+    from block_sparse_attention import block_sparse_attention
+    q, k, v, do, index, nums = _case(7, 1, 2, 512, 640, [3, 1, 4, 2], poison=False)
+    qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+    out = block_sparse_attention(qc, kc, vc, index.cuda(), 0, q2k_block_nums=nums.cuda())
+    out.backward(do.cuda())
+    bias = orc.block_sparse_to_attn_bias(index, 0, torch.full((5,), 128, dtype=torch.int32), 512, 640,
+                                         q2k_block_nums=nums)
+    _check(tuple(t.grad.float().cpu() for t in (qc, kc, vc)), q, k, v, do, bias, 1 / math.sqrt(128))

@@ -85,3 +85,19 @@ def test_mask_to_q2k_roundtrip_and_clamp():
     index, nums = block_mask_to_q2k(mask.cuda(), max_kv_blocks=16)
     e_index, e_nums = orc.mask_to_q2k(mask, 16)
     assert torch.equal(index.cpu(), e_index) and torch.equal(nums.cpu(), e_nums)
+
+
+@pytest.mark.parametrize("rows,cap", [(5, 3), (1024, 8), (5000, 256), (40000, 57)])
+def test_lpt_order_is_the_stable_descending_sort(rows, cap):
+    from block_sparse_attention import _cabi
+    lib = _cabi.load()
+    gen = torch.Generator().manual_seed(rows)
+    nums = torch.randint(-2, cap + 3, (rows,), generator=gen, dtype=torch.int32)
+    order = torch.empty(rows, dtype=torch.int32, device="cuda")
+    scratch = torch.empty(int(lib.bsa_lpt_order_scratch_ints(rows, cap)), dtype=torch.int32, device="cuda")
+    nc = nums.cuda()
+    rc = lib.bsa_lpt_order(nc.data_ptr(), rows, cap, order.data_ptr(), scratch.data_ptr(),
+                           torch.cuda.current_stream().cuda_stream)
+    assert rc == 0
+    expected = torch.sort(nums.clamp(0, cap), descending=True, stable=True).indices.int()
+    assert torch.equal(order.cpu(), expected)
