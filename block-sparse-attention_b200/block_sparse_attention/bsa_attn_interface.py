@@ -199,6 +199,18 @@ def _launch_fwd(*, q, k, v, out, lse, q2k_block_index, q2k_block_nums, block_siz
     args.pack_gqa = 1 if pack_gqa else 0
     args.splits = int(splits)
     args.softmax_scale = float(softmax_scale)
+    work_order = None
+    if q2k_block_nums is not None and q2k_block_nums.numel() > 2 * lib.bsa_num_sms(device.index or 0):
+        # variable counts: longest-first work order so that the persistent CTAs finish together
+        rows = q2k_block_nums.numel()
+        cap_sort = min(int(args.cap), 32000)
+        work_order = torch.empty(rows, dtype=torch.int32, device=device)
+        scratch = torch.empty(max(1, int(lib.bsa_lpt_order_scratch_ints(rows, cap_sort))), dtype=torch.int32,
+                              device=device)
+        with torch.cuda.device(device):
+            _cabi.check(lib.bsa_lpt_order(q2k_block_nums.data_ptr(), rows, cap_sort, work_order.data_ptr(),
+                                          scratch.data_ptr(), _cabi.stream_ptr(device)), "bsa_lpt_order")
+        args.work_order = work_order.data_ptr()
     partial_o = partial_lse = None
     if splits > 1:
         try:

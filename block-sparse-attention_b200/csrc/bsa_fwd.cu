@@ -126,6 +126,13 @@ __device__ __forceinline__ WorkItem decode_work(const FwdParams& p, int w) {
   return t;
 }
 
+// Work item of this CTA in band `band` of the work list: bands are walked back and forth (CTA c takes
+// c, 2G-1-c, 2G+c, ...), so that with a longest-first list every CTA gets a similar total.
+__device__ __forceinline__ int snake_work(int band) {
+  const int G = (int)gridDim.x, c = (int)blockIdx.x;
+  return band * G + ((band & 1) ? (G - 1 - c) : c);
+}
+
 // Valid token count of KV block j for (b, h): min(block_sizes[j], tokens physically left), >= 0.
 template <int BLK>
 __device__ __forceinline__ int block_len(const FwdParams& p, int b, int h, int j) {
@@ -224,7 +231,9 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     uint32_t q_cnt = 0;
     bool ok = true;
     PT_DECL
-    for (int w = blockIdx.x; w < p.num_work && ok; w += gridDim.x) {
+    for (int band = 0; band * (int)gridDim.x < p.num_work && ok; ++band) {
+      const int w = snake_work(band);
+      if (w >= p.num_work) continue;
       const WorkItem t = decode_work<BLK>(p, w);
       const int n_it = t.it_end - t.it_begin;
       if (n_it <= 0) continue;
@@ -317,7 +326,9 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint64_t k_desc0 = umma_desc_sw128(smem_u32(sKV), 0, 1024);                               // K-major view
     const uint64_t v_desc0 = umma_desc_sw128(smem_u32(sKV), FP8 ? 0u : (uint32_t)Cfg::kSlabBytes, 1024);  // MN-major
     PT_DECL
-    for (int w = blockIdx.x; w < p.num_work && ok; w += gridDim.x) {
+    for (int band = 0; band * (int)gridDim.x < p.num_work && ok; ++band) {
+      const int w = snake_work(band);
+      if (w >= p.num_work) continue;
       const WorkItem t = decode_work<BLK>(p, w);
       const int n_it = t.it_end - t.it_begin;
       if (n_it <= 0) continue;
@@ -426,7 +437,9 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     constexpr float kPBias = FP8 ? 7.0f : 0.0f;
     PT_DECL
 
-    for (int w = blockIdx.x; w < p.num_work && ok; w += gridDim.x) {
+    for (int band = 0; band * (int)gridDim.x < p.num_work && ok; ++band) {
+      const int w = snake_work(band);
+      if (w >= p.num_work) continue;
       const WorkItem t = decode_work<BLK>(p, w);
       const int n_it = t.it_end - t.it_begin;
       float m_cur = -INFINITY;  // running max, log2 domain (scale applied)

@@ -65,8 +65,8 @@ int bsa_num_sms(int device);
  * [splits, B, Hq, Sq, D] and its log-sum-exp to partial_lse [splits, B, Hq, Sq]; `out`/`lse` are not
  * touched and the caller runs bsa_fwd_combine afterwards.
  *
- * work_order: the persistent CTAs walk the tile rows in this order (CTA c takes entries c, c+G, c+2G, ...
- * of it, G = grid size).  NULL = natural order.
+ * work_order: the persistent CTAs walk the tile rows in this order (CTA c takes entries c, 2G-1-c, 2G+c, ...
+ * of it, G = grid size); a longest-first order balances skewed per-row counts.  NULL = natural order.
  *
  * dtype = BSA_DTYPE_E4M3 selects the Sage FP8 path: q, k, v hold e4m3 bytes, q_scale [B,H,Sq],
  * k_scale [B,H,ceil(Sk/16)] and v_scale [H,D] are the multiplicative dequantisation factors
