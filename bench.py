@@ -418,7 +418,10 @@ def main():
             "roofline": {"bound": "tensor", "kernel": "bsa_fwd_kernel<128,bf16>", "achieved": fwd_tf, "peak": peak,
                          "peak_burst": peak_burst, "peak_source": f"{peak_kind} (sustained bf16 GEMM; kernel timed "
                          "inside a long step)", "unit": "TFLOP/s", "frac": fwd_tf / peak,
-                         "frac_of_nominal_2250": fwd_tf / 2250.0, "traffic": None},
+                         "frac_of_nominal_2250": fwd_tf / 2250.0,
+                         # ncu dram__bytes_read+write of one forward launch on the cfg2_small capture (258 MB for
+                         # 2048 query tiles), scaled by the number of tiles (profiles/cfg2_small_tcgen05_kernels.md)
+                         "traffic": 258.1e6 * (Bp * H * Nq) / 2048.0 if args.workload == "cfg2" else None},
             "gpu_launches": args.steps * (1 if args.fwd_only else 9),
             "clocks": clocks,
         }

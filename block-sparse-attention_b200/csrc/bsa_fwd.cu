@@ -508,7 +508,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const uint32_t t_row = tS[grp] + lane_base;
         const bool masked = (BLK == 128) ? (len0 < 128) : (len0 < 64 || len1 < 64);  // warp-uniform
         float bm;
-        if (FP8 || masked) {
+        if (masked) {
           tmem_ld32(t_row + 0, su + 0);
           tmem_ld32(t_row + 32, su + 32);
           tmem_ld32(t_row + 64, su + 64);
@@ -546,6 +546,33 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               m1 = fmax3(m1, sv[(c + 2) & 127], sv[(c + 3) & 127]);
             }
             bm = fmaxf(m0, m1) * p.scale_log2;
+          }
+        } else if (FP8) {
+          // common case, e4m3: group maxima (16 tokens share a K scale) of the first half while the second
+          // half is still arriving
+          tmem_ld32(t_row + 0, su + 0);
+          tmem_ld32(t_row + 32, su + 32);
+          tmem_wait_ld();
+          tmem_ld32(t_row + 64, su + 64);
+          tmem_ld32(t_row + 96, su + 96);
+          bm = -INFINITY;
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            float gm = fmax3(sv[g * 16], sv[g * 16 + 1], sv[g * 16 + 2]);
+#pragma unroll
+            for (int c = 3; c < 15; c += 2) gm = fmax3(gm, sv[g * 16 + c], sv[g * 16 + c + 1]);
+            gm = fmaxf(gm, sv[g * 16 + 15]);
+            bm = fmaxf(bm, gm * ksc[g]);
+          }
+          tmem_wait_ld();
+          PT_MARK(2)
+#pragma unroll
+          for (int g = 4; g < 8; ++g) {
+            float gm = fmax3(sv[g * 16], sv[g * 16 + 1], sv[g * 16 + 2]);
+#pragma unroll
+            for (int c = 3; c < 15; c += 2) gm = fmax3(gm, sv[g * 16 + c], sv[g * 16 + c + 1]);
+            gm = fmaxf(gm, sv[g * 16 + 15]);
+            bm = fmaxf(bm, gm * ksc[g]);
           }
         } else {
           // common case: two 64-column halves; the second arrives while the maximum of the first is taken
@@ -602,6 +629,8 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         // ---- exponentials, row sum, P to tensor memory
         float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
         if (FP8) {
+          const uint64_t nm2 = pack2(neg_m, neg_m);
+          uint64_t s0 = pack2(0.f, 0.f), s1 = s0;
 #pragma unroll
           for (int c4 = 0; c4 < 4; ++c4) {
             uint32_t pk[8];
@@ -609,16 +638,38 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             for (int e = 0; e < 8; ++e) {
               const int c = c4 * 32 + e * 4;
               const float sc = ksc[c >> 4];
-              // masked columns hold -inf; a zero scale there would make NaN, so select explicitly
-              float x0 = (sv[c] == -INFINITY) ? 0.f : ex2_approx(fmaf(sv[c], sc, neg_m));
-              float x1 = (sv[c + 1] == -INFINITY) ? 0.f : ex2_approx(fmaf(sv[c + 1], sc, neg_m));
-              float x2 = (sv[c + 2] == -INFINITY) ? 0.f : ex2_approx(fmaf(sv[c + 2], sc, neg_m));
-              float x3 = (sv[c + 3] == -INFINITY) ? 0.f : ex2_approx(fmaf(sv[c + 3], sc, neg_m));
-              a0 += x0; a1 += x1; a2 += x2; a3 += x3;
+              float x0, x1, x2, x3;
+              if (masked) {
+                // masked columns hold -inf; a zero scale there would make NaN, so select explicitly
+                x0 = (sv[c] == -INFINITY) ? 0.f : ex2_approx(fmaf(sv[c], sc, neg_m));
+                x1 = (sv[c + 1] == -INFINITY) ? 0.f : ex2_approx(fmaf(sv[c + 1], sc, neg_m));
+                x2 = (sv[c + 2] == -INFINITY) ? 0.f : ex2_approx(fmaf(sv[c + 2], sc, neg_m));
+                x3 = (sv[c + 3] == -INFINITY) ? 0.f : ex2_approx(fmaf(sv[c + 3], sc, neg_m));
+              } else {
+                const uint64_t sc2 = pack2(sc, sc);
+                unpack2(ffma2(pack2(sv[c], sv[c + 1]), sc2, nm2), x0, x1);
+                unpack2(ffma2(pack2(sv[c + 2], sv[c + 3]), sc2, nm2), x2, x3);
+                x0 = ex2_approx(x0);
+                x1 = ex2_approx(x1);
+                x2 = ex2_approx(x2);
+                x3 = ex2_approx(x3);
+              }
+              s0 = fadd2(s0, pack2(x0, x1));
+              s1 = fadd2(s1, pack2(x2, x3));
               pk[e] = pack_e4m3x4(x0, x1, x2, x3);
+            }
+            if (c4 == 2) {
+              // first half of P_s (two MMA k steps) released on its own barrier, its stores long landed
+              tmem_wait_st();
+              tc_fence_before();
+              mbar_arrive(BAR(kPHalf + grp));
             }
             tmem_st8(tS[grp] + lane_base + c4 * 8, pk);
           }
+          float y0, y1, y2, y3;
+          unpack2(s0, y0, y1);
+          unpack2(s1, y2, y3);
+          a0 = y0; a1 = y1; a2 = y2; a3 = y3;
         } else {
           const uint64_t sc2 = pack2(p.scale_log2, p.scale_log2);
           const uint64_t nm2 = pack2(neg_m, neg_m);
@@ -662,7 +713,6 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         PT_MARK(4)
         tmem_wait_st();
         tc_fence_before();
-        if (FP8) mbar_arrive(BAR(kPHalf + grp));
         mbar_arrive(BAR(kPFull + grp));
         PT_MARK(5)
       }

@@ -250,3 +250,31 @@ def test_medium_uniform_many_tiles():
     ref_out, ref_lse = orc.attention_gathered(q, k, v, index, 0, nums=nums, heads=[0, 3])
     sel = [0, 3]
     _check(out[:, sel], lse[:, sel], ref_out[:, sel], ref_lse[:, sel], q, k, v)
+
+
+def test_cuda_graph_capture_on_a_side_stream_bf16_and_fp8():
+    """calls are capturable and side-stream safe (tests/test_bsa_fp8_blk128.py:372-397,
+    tests/test_sm100_blk128_sync.py:37-63): no host synchronisation, no read-back on the call path."""
+    from block_sparse_attention import bsa_fp8_blk128_fwd, quantize_sage_bhsd
+    q, k, v, index, nums, _ = _random_case(23, 1, 2, 2, 512, 1024, 128, [3, 8, 0, 5])
+    qc, kc, vc, ic, nc = _cuda(q, k, v, index, nums)
+    eager_out, eager_lse = _fwd(qc, kc, vc, ic, 0, q2k_block_nums=nc, return_lse=True, sparse_block_size=128)
+    quant = quantize_sage_bhsd(qc, kc, vc)
+    eager_fp8 = bsa_fp8_blk128_fwd(*quant, ic, 0, q2k_block_nums=nc, kv_splits=2)
+    torch.cuda.synchronize()
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        _fwd(qc, kc, vc, ic, 0, q2k_block_nums=nc, return_lse=True, sparse_block_size=128)  # warm-up on the stream
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=side):
+            g_out, g_lse = _fwd(qc, kc, vc, ic, 0, q2k_block_nums=nc, return_lse=True, sparse_block_size=128)
+            g_fp8 = bsa_fp8_blk128_fwd(*quant, ic, 0, q2k_block_nums=nc, kv_splits=2)
+        g_out.zero_()
+        g_fp8.zero_()
+        graph.replay()
+        graph.replay()
+    side.synchronize()
+    torch.cuda.current_stream().wait_stream(side)
+    assert torch.equal(g_out, eager_out) and torch.equal(g_lse, eager_lse)
+    assert torch.equal(g_fp8, eager_fp8)
