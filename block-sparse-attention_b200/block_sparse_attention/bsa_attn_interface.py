@@ -364,7 +364,7 @@ def bsa_attn_fwd(
 # Sage FP8 forward
 # --------------------------------------------------------------------------------------------------
 def _bsa_fp8_blk128_fwd(q_fp8, k_fp8, v_fp8, q_sfs, k_sfs, v_sfs, q2k_block_index, topk_num, softmax_scale,
-                        block_sizes, q2k_block_nums, kv_splits):
+                        block_sizes, q2k_block_nums, kv_splits, blk=128):
     assert isinstance(kv_splits, int) and not isinstance(kv_splits, bool), "kv_splits must be an int"
     assert 1 <= kv_splits <= 256, "kv_splits must be in [1, 256]"
     for t in (q_fp8, k_fp8, v_fp8):
@@ -387,7 +387,7 @@ def _bsa_fp8_blk128_fwd(q_fp8, k_fp8, v_fp8, q_sfs, k_sfs, v_sfs, q2k_block_inde
     v_sc = v_sfs.reshape(H, D).contiguous()
     q2k_block_index, block_sizes, q2k_block_nums = _normalise_metadata(
         q2k_block_index, block_sizes, q2k_block_nums, device)
-    Nq, Nkv = _ceil_div(Sq, 128), _ceil_div(Sk, 128)
+    Nq, Nkv = _ceil_div(Sq, blk), _ceil_div(Sk, blk)
     assert q2k_block_index.shape[:3] == (B, H, Nq)
     if q2k_block_nums is not None:
         assert q2k_block_nums.shape == (B, H, Nq)
@@ -398,7 +398,7 @@ def _bsa_fp8_blk128_fwd(q_fp8, k_fp8, v_fp8, q_sfs, k_sfs, v_sfs, q2k_block_inde
         softmax_scale = 1.0 / math.sqrt(D)
     out = torch.empty((B, H, Sq, D), dtype=torch.bfloat16, device=device)
     _launch_fwd(q=q8, k=k8, v=v8, out=out, lse=None, q2k_block_index=q2k_block_index,
-                q2k_block_nums=q2k_block_nums, block_sizes=block_sizes, bs_strides=bs_strides, blk=128,
+                q2k_block_nums=q2k_block_nums, block_sizes=block_sizes, bs_strides=bs_strides, blk=blk,
                 block_sparse_num=topk_num if q2k_block_nums is None else 0, pack_gqa=False, splits=kv_splits,
                 softmax_scale=softmax_scale, dtype_code=_cabi.BSA_DTYPE_E4M3, q_scale=q_sc, k_scale=k_sc,
                 v_scale=v_sc)
@@ -441,9 +441,11 @@ def bsa_fp8_blk64_fwd(
     block_sizes: Optional[torch.Tensor] = None,
     q2k_block_nums: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
-    """Sage FP8 forward with 64-token blocks (reference bsa_attn_interface.py:2953-3182).
-    Not built in this engine yet: raises AssertionError."""
-    raise AssertionError("Sage FP8 with sparse_block_size=64 is not built; use sparse_block_size=128")
+    """Sage FP8 forward with 64-token blocks (reference bsa_attn_interface.py:2953-3182): same scale
+    recipe and metadata as the 128-block entry; returns one BF16 BHSD tensor.  The split count is chosen
+    here (one split; the reference's automatic FP8 split policy targets its own kernel's occupancy)."""
+    return _bsa_fp8_blk128_fwd(q_fp8, k_fp8, v_fp8, q_sfs, k_sfs, v_sfs, q2k_block_index, topk_num,
+                               softmax_scale, block_sizes, q2k_block_nums, 1, blk=64)
 
 
 def bsa_fp8_fwd(

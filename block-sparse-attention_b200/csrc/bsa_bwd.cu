@@ -35,6 +35,8 @@ namespace bsa {
 constexpr int kBwdThreads = 320;
 constexpr int kBwdMmaWarp = 8;
 constexpr int kBwdLoadWarp = 9;
+constexpr int kDkvThreads = 352;  // dK/dV kernel: warps 8 and 9 issue MMAs, warp 10 loads
+constexpr int kDkvLoadWarp = 10;
 constexpr int kTile = 128 * 128 * 2;  // bytes of one bf16 128x128 tile
 constexpr int kSlab = 128 * 128;      // bytes of one 64-column slab
 
@@ -461,7 +463,7 @@ constexpr int kDkvStages = 4;
 constexpr int kStatSlots = 4;
 constexpr int kDkvSmem = 2 * kTile + kDkvStages * kTile + kStatSlots * 1024 + BwdSmem::kBarBytes + BwdSmem::kMisc;
 
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(kDkvThreads, 1)
 bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const BwdParams p) {
   constexpr int NS = kDkvStages;
@@ -489,16 +491,16 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   if (threadIdx.x == 0) {
     s_abort = 0;
     mbar_init(BAR(kKvFull), 1);
-    mbar_init(BAR(kKvEmpty), 1);
+    mbar_init(BAR(kKvEmpty), 2);  // one commit per issuing warp
     for (int i = 0; i < NS; ++i) {
       mbar_init(BAR(kRFull + i), 1);
-      mbar_init(BAR(kREmpty + i), 1);
+      mbar_init(BAR(kREmpty + i), 2);  // released by both issuing warps
     }
     mbar_init(BAR(kSFull), 1);
     mbar_init(BAR(kDpFull), 1);
     mbar_init(BAR(kPFull), 256);
     mbar_init(BAR(kDsFull), 256);
-    mbar_init(BAR(kFinal), 1);
+    mbar_init(BAR(kFinal), 2);
     mbar_init(BAR(kFree), 256);
     mbar_fence_init();
     fence_proxy_async_smem();
@@ -524,7 +526,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     return t;
   };
 
-  if (warp == kBwdLoadWarp) {
+  if (warp == kDkvLoadWarp) {
     uint32_t r_cnt = 0, kv_cnt = 0, tile_cnt = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
@@ -571,8 +573,15 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
     }
-  } else if (warp == kBwdMmaWarp) {
-    uint32_t r_cnt = 0, kv_cnt = 0, p_cnt = 0, ds_cnt = 0, free_cnt = 0;
+  } else if (warp == kBwdMmaWarp || warp == kBwdMmaWarp + 1) {
+    // Two issuing warps (tcgen05.mma issue stalls the issuing thread at the execution rate, so a single
+    // issuer leaves the tensor pipe idle during its own barrier bookkeeping):
+    //   issuer 0: S^T_i = K Q_i^T and dV += P^T_i dO_i   (tensor-memory region S/P and dV)
+    //   issuer 1: dP^T_i = V dO_i^T and dK += dS^T_i Q_i (tensor-memory region dP/dS and dK)
+    // Each issuer visits every ring position in increasing order (a parity wait is never more than one
+    // phase behind) and every ring stage is released by one commit of each issuer.
+    const int who = warp - kBwdMmaWarp;
+    uint32_t r_cnt = 0, kv_cnt = 0, in_cnt = 0, free_cnt = 0;
     bool ok = true, first_item = true;
     const uint64_t k_desc = desc_k_major(smem_u32(sK)), v_desc = desc_k_major(smem_u32(sV));
     const uint64_t ring_k = desc_k_major(smem_u32(sRing)), ring_mn = desc_mn_major(smem_u32(sRing));
@@ -593,66 +602,82 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         PT_MARK(2)
         return r;
       };
-      auto issue_s = [&](int i) -> bool {  // S^T = K Q_i^T
-        if (!wait_full(base + 2 * i)) return false;
-        tc_fence_after();
-        if (lane == 0) {
-          mma_ss_kk(tS, k_desc, ring_k + stage_of(base + 2 * i) * kTileDescStep, false);
+      if (who == 0) {
+        // ---- issuer 0
+        ok = wait_full(base);
+        if (ok && lane == 0) {
+          mma_ss_kk(tS, k_desc, ring_k + stage_of(base) * kTileDescStep, false);  // S^T_0
           umma_commit(BAR(kSFull));
+          umma_commit(BAR(kREmpty + stage_of(base)));
         }
         __syncwarp();
-        return true;
-      };
-      auto issue_dp = [&](int i) -> bool {  // dP^T = V dO_i^T
-        if (!wait_full(base + 2 * i + 1)) return false;
-        tc_fence_after();
-        if (lane == 0) {
-          mma_ss_kk(tdP, v_desc, ring_k + stage_of(base + 2 * i + 1) * kTileDescStep, false);
-          umma_commit(BAR(kDpFull));
-        }
-        __syncwarp();
-        return true;
-      };
-      ok = issue_s(0);
-      if (ok) ok = issue_dp(0);
-      for (int i = 0; i < T && ok; ++i) {
-        PT_MARK(0)
-        ok = mbar_wait(BAR(kPFull), p_cnt & 1, wctx, 512);  // P^T_i in tensor memory
-        if (!ok) break;
-        PT_MARK(3)
-        ++p_cnt;
-        if (i == 0 && !first_item) {  // previous item's epilogue has drained dV / dK
-          ok = mbar_wait(BAR(kFree), free_cnt & 1, wctx, 513);
+        for (int i = 0; i < T && ok; ++i) {
+          ok = wait_full(base + 2 * i + 1);  // dO_i
           if (!ok) break;
-          ++free_cnt;
-        }
-        tc_fence_after();
-        if (lane == 0) {
-          const uint32_t sd = stage_of(base + 2 * i + 1);
-          mma_ts_kmn(tdV, tS, tS + 64u, ring_mn + sd * kTileDescStep, i > 0);  // dV += P^T dO_i
-          umma_commit(BAR(kREmpty + sd));
-        }
-        __syncwarp();
-        if (i + 1 < T) {
-          ok = issue_s(i + 1);
+          PT_MARK(0)
+          ok = mbar_wait(BAR(kPFull), in_cnt & 1, wctx, 512);  // P^T_i in tensor memory
           if (!ok) break;
+          PT_MARK(3)
+          ++in_cnt;
+          if (i == 0 && !first_item) {  // the previous item's epilogue has drained dV
+            ok = mbar_wait(BAR(kFree), free_cnt & 1, wctx, 513);
+            if (!ok) break;
+          }
+          if (i == 0 && !first_item) ++free_cnt;
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t sd = stage_of(base + 2 * i + 1);
+            mma_ts_kmn(tdV, tS, tS + 64u, ring_mn + sd * kTileDescStep, i > 0);  // dV += P^T dO_i
+            umma_commit(BAR(kREmpty + sd));
+          }
+          __syncwarp();
+          if (i + 1 < T) {
+            ok = wait_full(base + 2 * i + 2);  // Q_{i+1}
+            if (!ok) break;
+            if (lane == 0) {
+              const uint32_t sq = stage_of(base + 2 * i + 2);
+              mma_ss_kk(tS, k_desc, ring_k + sq * kTileDescStep, false);  // S^T_{i+1}, after dV_i in program order
+              umma_commit(BAR(kSFull));
+              umma_commit(BAR(kREmpty + sq));
+            }
+            __syncwarp();
+          }
         }
-        PT_MARK(0)
-        ok = mbar_wait(BAR(kDsFull), ds_cnt & 1, wctx, 514);  // dS^T_i in tensor memory
-        if (!ok) break;
-        PT_MARK(4)
-        ++ds_cnt;
-        tc_fence_after();
-        if (lane == 0) {
-          const uint32_t sq = stage_of(base + 2 * i);
-          mma_ts_kmn(tdK, tdP, tdP + 64u, ring_mn + sq * kTileDescStep, i > 0);  // dK += dS^T Q_i
-          umma_commit(BAR(kREmpty + sq));
+      } else {
+        // ---- issuer 1
+        for (int i = 0; i < T && ok; ++i) {
+          ok = wait_full(base + 2 * i);  // Q_i (needed for dK_i; visited first to keep the waits in order)
+          if (ok) ok = wait_full(base + 2 * i + 1);  // dO_i
+          if (!ok) break;
+          if (lane == 0) {
+            const uint32_t sd = stage_of(base + 2 * i + 1);
+            // dP^T_i: in program order after dK_{i-1}, which read dS^T_{i-1} from the same columns
+            mma_ss_kk(tdP, v_desc, ring_k + sd * kTileDescStep, false);
+            umma_commit(BAR(kDpFull));
+            umma_commit(BAR(kREmpty + sd));
+          }
+          __syncwarp();
+          PT_MARK(0)
+          ok = mbar_wait(BAR(kDsFull), in_cnt & 1, wctx, 514);  // dS^T_i in tensor memory
+          if (!ok) break;
+          PT_MARK(4)
+          ++in_cnt;
+          if (i == 0 && !first_item) {  // the previous item's epilogue has drained dK
+            ok = mbar_wait(BAR(kFree), free_cnt & 1, wctx, 515);
+            if (!ok) break;
+          }
+          if (i == 0 && !first_item) ++free_cnt;
+          tc_fence_after();
+          if (lane == 0) {
+            const uint32_t sq = stage_of(base + 2 * i);
+            mma_ts_kmn(tdK, tdP, tdP + 64u, ring_mn + sq * kTileDescStep, i > 0);  // dK += dS^T Q_i
+            umma_commit(BAR(kREmpty + sq));
+          }
+          __syncwarp();
         }
-        __syncwarp();
-        if (i + 1 < T) ok = issue_dp(i + 1);
       }
       if (!ok) break;
-      if (lane == 0) {
+      if (lane == 0) {  // both issuers: their share of the accumulators is final, K / V no longer needed
         umma_commit(BAR(kFinal));
         umma_commit(BAR(kKvEmpty));
       }
@@ -661,7 +686,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       first_item = false;
     }
     PT_MARK(0)
-    PTB_FLUSH(64 + 16)
+    if (who == 0) { PTB_FLUSH(64 + 16) } else { PTB_FLUSH(64 + 24) }
   } else if (warp < 8) {
     const int grp = warp >> 2;
     const int row = threadIdx.x & 127;  // kv token inside the block = tensor-memory lane
@@ -911,7 +936,7 @@ extern "C" int bsa_bwd(const bsa_bwd_args* a, void* cuda_stream) {
   bwd_dq_kernel<<<grid_q, kBwdThreads, kDqSmem, st>>>(tq, tdo, tk, tv, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "bwd dQ launch: %s", cudaGetErrorString(e));
-  bwd_dkv_kernel<<<grid_kv, kBwdThreads, kDkvSmem, st>>>(tq, tdo, tk, tv, p);
+  bwd_dkv_kernel<<<grid_kv, kDkvThreads, kDkvSmem, st>>>(tq, tdo, tk, tv, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "bwd dK/dV launch: %s", cudaGetErrorString(e));
   return BSA_OK;

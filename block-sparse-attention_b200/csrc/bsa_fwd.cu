@@ -464,6 +464,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         // mask metadata for this KV iteration
         int len0 = BLK, len1 = BLK;
         int j0 = 0;
+        int j1 = 0;
         if (need_mask_meta || FP8) {
           const int it = t.it_begin + i;
           if (BLK == 128) {
@@ -472,7 +473,9 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           } else {
             j0 = t.row[2 * it];
             len0 = block_len<BLK>(p, t.b, t.hkv, j0);
-            len1 = (2 * it + 1 < t.count) ? block_len<BLK>(p, t.b, t.hkv, t.row[2 * it + 1]) : 0;
+            const bool live1 = 2 * it + 1 < t.count;
+            j1 = live1 ? t.row[2 * it + 1] : j0;
+            len1 = live1 ? block_len<BLK>(p, t.b, t.hkv, j1) : 0;
           }
         } else if (BLK == 64) {
           const int it = t.it_begin + i;
@@ -480,13 +483,14 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         float ksc[8];
         if (FP8) {
-          // eight 16-token scale groups of this 128-block
+          // eight 16-token scale groups of this 128-token tile: one 128-block, or four of each 64-block
           const int ngroups = (p.Sk + 15) / 16;
           const float* ks = p.k_scale + ((long long)t.b * p.Hkv + t.hkv) * ngroups;
 #pragma unroll
           for (int g = 0; g < 8; ++g) {
-            const int gi = j0 * 8 + g;
-            ksc[g] = (j0 >= 0 && gi < ngroups) ? ks[gi] * (q_row_scale * p.scale_log2) : 0.f;
+            const int jb = (BLK == 128 || g < 4) ? j0 : j1;
+            const int gi = (BLK == 128) ? jb * 8 + g : jb * 4 + (g & 3);
+            ksc[g] = (jb >= 0 && gi < ngroups) ? ks[gi] * (q_row_scale * p.scale_log2) : 0.f;
           }
         }
 
@@ -883,8 +887,6 @@ extern "C" int bsa_fwd(const bsa_fwd_args* a, void* cuda_stream) {
   const int G = a->Hq / a->Hkv;
   if (fp8 && (G != 1 || !a->q_scale || !a->k_scale || !a->v_scale))
     return set_error(BSA_ERR_INVALID, "bsa_fwd: FP8 path needs MHA and the three scale tensors");
-  if (fp8 && a->blk != 128)
-    return set_error(BSA_ERR_UNSUPPORTED, "bsa_fwd: FP8 64-token blocks not built");
   const int packed = a->pack_gqa != 0 && G > 1;
   if (packed && (a->blk % G) != 0) return set_error(BSA_ERR_INVALID, "bsa_fwd: pack_gqa needs blk %% group == 0");
 
@@ -965,8 +967,11 @@ extern "C" int bsa_fwd(const bsa_fwd_args* a, void* cuda_stream) {
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(cuda_stream);
   const bool split = a->splits > 1;
   if (fp8) {
-    return split ? launch_fwd<128, true, true>(*a, p, tq, tk, tv, to, num_sms, stream)
-                 : launch_fwd<128, true, false>(*a, p, tq, tk, tv, to, num_sms, stream);
+    if (a->blk == 128)
+      return split ? launch_fwd<128, true, true>(*a, p, tq, tk, tv, to, num_sms, stream)
+                   : launch_fwd<128, true, false>(*a, p, tq, tk, tv, to, num_sms, stream);
+    return split ? launch_fwd<64, true, true>(*a, p, tq, tk, tv, to, num_sms, stream)
+                 : launch_fwd<64, true, false>(*a, p, tq, tk, tv, to, num_sms, stream);
   }
   if (a->blk == 128) {
     return split ? launch_fwd<128, false, true>(*a, p, tq, tk, tv, to, num_sms, stream)

@@ -117,3 +117,36 @@ def test_softmax_scale_argument():
     q, k, v, index, nums, sizes = _make(4, 1, 1, 256, 256, 2)
     out, quant = _run(q, k, v, index, 2, None, None, scale=0.03)
     _accuracy(out, q, k, v, quant, index, 2, None, None, scale=0.03)
+
+
+@pytest.mark.parametrize("Sq,Sk,topk,variable,sizes_mode", [(256, 512, 5, False, 0), (200, 1000, 7, True, 3),
+                                                            (64, 2048, 32, True, 1)])
+def test_blk64_entry_point(Sq, Sk, topk, variable, sizes_mode):
+    """Sage FP8 with 64-token blocks (bsa_fp8_blk64_fwd / bsa_fp8_fwd(sparse_block_size=64))."""
+    from block_sparse_attention import bsa_fp8_fwd, quantize_sage_bhsd
+    gen = torch.Generator().manual_seed(Sq + Sk)
+    B, H = 2, 2
+    q = torch.randn(B, H, Sq, 128, generator=gen).bfloat16()
+    k = (torch.randn(B, H, Sk, 128, generator=gen) + torch.randn(1, 1, 1, 128, generator=gen)).bfloat16()
+    v = torch.randn(B, H, Sk, 128, generator=gen).bfloat16()
+    nq, nk = math.ceil(Sq / 64), math.ceil(Sk / 64)
+    index = torch.stack([torch.randperm(nk, generator=gen)[:topk] for _ in range(B * H * nq)])
+    index = index.reshape(B, H, nq, topk).int()
+    nums = sizes = None
+    if variable:
+        nums = (torch.arange(B * H * nq) % (topk + 1)).reshape(B, H, nq).int()
+        index = index.masked_fill(torch.arange(topk) >= nums[..., None], 0x3FFFFFFF)
+    if sizes_mode:
+        shape = {1: (nk,), 3: (B, H, nk)}[sizes_mode]
+        sizes = torch.randint(1, 65, shape, generator=gen, dtype=torch.int32)
+        sizes[..., -1].clamp_(max=Sk - (nk - 1) * 64)
+    quant = quantize_sage_bhsd(q.cuda(), k.cuda(), v.cuda())
+    out = bsa_fp8_fwd(*quant, index.cuda(), topk, sparse_block_size=64,
+                      block_sizes=None if sizes is None else sizes.cuda(),
+                      q2k_block_nums=None if nums is None else nums.cuda())
+    o = out.float().cpu()
+    assert torch.isfinite(o).all()
+    deq = orc.sage_dequantize(*(t.cpu() for t in quant))
+    ref = orc.attention_gathered(*deq, index, topk, nums=nums, sizes=sizes, blk=64, return_lse=False)
+    rel, mx = orc.fp8_accuracy(o, ref)
+    assert mx < 0.15 and rel < 0.029, (rel, mx)

@@ -278,3 +278,31 @@ def test_cuda_graph_capture_on_a_side_stream_bf16_and_fp8():
     torch.cuda.current_stream().wait_stream(side)
     assert torch.equal(g_out, eager_out) and torch.equal(g_lse, eager_lse)
     assert torch.equal(g_fp8, eager_fp8)
+
+
+def test_block_sizes_larger_than_the_physical_tail_do_not_unmask_padding():
+    """a provided extent beyond the tokens that exist must not attend to padding
+    (tests/test_bsa_fp8_blk128.py:178-201)."""
+    q, k, v, index, nums, _ = _random_case(29, 1, 2, 2, 256, 1000, 128, [8])
+    sizes = torch.full((8,), 128, dtype=torch.int32)  # last block really has 104 tokens
+    out, lse = _fwd(*_cuda(q, k, v, index), 0, block_sizes=sizes.cuda(), q2k_block_nums=nums.cuda(), return_lse=True,
+                    sparse_block_size=128)
+    ref_out, ref_lse = orc.attention_gathered(q, k, v, index, 0, nums=nums)
+    _check(out, lse, ref_out, ref_lse, q, k, v)
+
+
+def test_batch_stride_beyond_2_to_the_31_elements():
+    """views whose batch stride exceeds 2^31 elements (tests/test_flash_fwd.py:1641-1722): 64-bit strides end to end."""
+    B, H, S = 2, 1, 256
+    stride_b = (1 << 31) + 4096
+    store = torch.empty(stride_b + H * S * 128, dtype=torch.bfloat16, device="cuda")
+    gen = torch.Generator().manual_seed(31)
+    q = torch.randn(B, H, S, 128, generator=gen).bfloat16()
+    k = torch.randn(B, H, S, 128, generator=gen).bfloat16()
+    v = torch.randn(B, H, S, 128, generator=gen).bfloat16()
+    k_view = store.as_strided((B, H, S, 128), (stride_b, S * 128, 128, 1))
+    k_view.copy_(k.cuda())
+    index = torch.tensor([[0, 1], [1, 0]], dtype=torch.int32).expand(B, H, 2, 2).contiguous()
+    out, lse = _fwd(q.cuda(), k_view, v.cuda(), index.cuda(), 2, return_lse=True, sparse_block_size=128)
+    ref_out, ref_lse = orc.attention_gathered(q, k, v, index, 2)
+    _check(out, lse, ref_out, ref_lse, q, k, v)
