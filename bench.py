@@ -10,8 +10,9 @@ sparse-effective TFLOPS, counting active (q block, kv block) pairs only: 4*128^2
 and 10*128^2*128 backward (the reference's convention).  With N > 1 every rank owns its own batch slice
 of a global batch of 2N (sharding by (batch, head), no collective on the data path): weak scaling.
 
-The JSON line also carries: `e2e` (same metric through the public API with pinned host buffers, H2D of
-q/k/v/dO and D2H of O/LSE/dQ/dK/dV inside the timed region), `roofline` of the forward kernel against the
+The JSON line also carries: `e2e` (same metric through the public host-memory entry `HostPipeline`, pinned
+host buffers, H2D of q/k/v/dO and D2H of O/LSE/dQ/dK/dV inside the timed region, head chunks pipelined over
+three streams), `roofline` of the forward kernel against the
 measured dense BF16 peak (MEASURED_PEAKS.json when present), `roofline_bwd`, `cpu_baseline` (the CPU
 oracle on a bounded sample of the same workload, rank 0, N=1 only), `clocks` sampled with nvidia-smi
 during the timed region and `gpu_launches`.
@@ -368,15 +369,15 @@ def main():
         h2d = sum(t.numel() * t.element_size() for t in host.values())
         d2h = sum(t.numel() * t.element_size() for t in host_out.values()) + host_lse.numel() * 4
 
+        from block_sparse_attention.host_pipeline import HostPipeline
+        # the public host-memory entry: head chunks pipelined over copy / compute / copy streams
+        pipe = HostPipeline(Bp, H, S, S, idx, count, heads_per_chunk=8)
+        host_res = {"out": host_out["o"], "lse": host_lse, "dq": host_out["dq"], "dk": host_out["dk"],
+                    "dv": host_out["dv"]}
+        host_src = {"q": host["q"], "k": host["k"], "v": host["v"], "dout": host["do"]}
+
         def e2e_step():
-            qd, kd, vd, dod = (host[n].to(dev, non_blocking=True) for n in ("q", "k", "v", "do"))
-            o, l = bsa_attn_fwd(qd, kd, vd, idx, count, return_lse=True, sparse_block_size=BLK)
-            gq, gk, gv = bsa_attn_bwd(dod, qd, kd, vd, o, l, idx, count, sparse_block_size=BLK)
-            host_out["o"].copy_(o, non_blocking=True)
-            host_lse.copy_(l, non_blocking=True)
-            host_out["dq"].copy_(gq, non_blocking=True)
-            host_out["dk"].copy_(gk, non_blocking=True)
-            host_out["dv"].copy_(gv, non_blocking=True)
+            pipe.run(host_src, host_res)
 
         e2e_step()
         barrier()

@@ -15,6 +15,7 @@ _EXPORTS = {
     "check_device_status": ".bsa_attn_interface",
     "quantize_sage_bhsd": ".bsa_fp8_quant",
     "block_sparse_attention": ".autograd",
+    "HostPipeline": ".host_pipeline",
     "BlockSparseAttentionFunction": ".autograd",
 }
 

@@ -151,3 +151,23 @@ def test_autograd_function_matches_oracle_gradients():
     bias = orc.block_sparse_to_attn_bias(index, 0, torch.full((5,), 128, dtype=torch.int32), 512, 640,
                                          q2k_block_nums=nums)
     _check(tuple(t.grad.float().cpu() for t in (qc, kc, vc)), q, k, v, do, bias, 1 / math.sqrt(128))
+
+
+def test_host_pipeline_matches_direct_calls():
+    """pinned host tensors in, pinned host tensors out, head chunks pipelined over three streams."""
+    from block_sparse_attention import HostPipeline, bsa_attn_bwd, bsa_attn_fwd
+    q, k, v, do, index, nums = _case(11, 2, 4, 512, 768, [3, 1, 5, 2, 0, 4], poison=False)
+    ic, nc = index.cuda(), nums.cuda()
+    host_in = {"q": q.pin_memory(), "k": k.pin_memory(), "v": v.pin_memory(), "dout": do.pin_memory()}
+    host_out = {"out": torch.empty_like(q).pin_memory(), "lse": torch.empty(2, 4, 512).pin_memory(),
+                "dq": torch.empty_like(q).pin_memory(), "dk": torch.empty_like(k).pin_memory(),
+                "dv": torch.empty_like(v).pin_memory()}
+    pipe = HostPipeline(2, 4, 512, 768, ic, 0, q2k_block_nums=nc, heads_per_chunk=2)
+    pipe.run(host_in, host_out)
+    pipe.run(host_in, host_out)  # slots are reused
+    torch.cuda.synchronize()
+    qc, kc, vc, doc = (t.cuda() for t in (q, k, v, do))
+    out, lse = bsa_attn_fwd(qc, kc, vc, ic, 0, q2k_block_nums=nc, return_lse=True, sparse_block_size=128)
+    dq, dk, dv = bsa_attn_bwd(doc, qc, kc, vc, out, lse, ic, 0, q2k_block_nums=nc, sparse_block_size=128)
+    for name, ref in (("out", out), ("lse", lse), ("dq", dq), ("dk", dk), ("dv", dv)):
+        assert torch.equal(host_out[name], ref.cpu()), name
