@@ -18,6 +18,7 @@ LIB_PATH = os.environ.get("BSA_B200_LIB") or os.path.join(_HERE, "libbsa_b200.so
 
 BSA_DTYPE_BF16 = 0
 BSA_DTYPE_E4M3 = 1
+BSA_DTYPE_F16 = 2
 
 _c_i64x3 = ctypes.c_int64 * 3
 
@@ -81,6 +82,7 @@ class BwdArgs(ctypes.Structure):
         ("q2k_nums", ctypes.c_void_p),
         ("csr_offsets", ctypes.c_void_p),
         ("csr_indices", ctypes.c_void_p),
+        ("block_sizes", ctypes.c_void_p),
         ("workspace", ctypes.c_void_p),
         ("status", ctypes.c_void_p),
         ("workspace_bytes", ctypes.c_int64),
@@ -92,6 +94,8 @@ class BwdArgs(ctypes.Structure):
         ("dq_stride", _c_i64x3),
         ("dk_stride", _c_i64x3),
         ("dv_stride", _c_i64x3),
+        ("bs_stride_b", ctypes.c_int64),
+        ("bs_stride_h", ctypes.c_int64),
         ("blk", ctypes.c_int32),
         ("B", ctypes.c_int32),
         ("H", ctypes.c_int32),

@@ -116,6 +116,13 @@ def sm100_blk128_bwd_default_bucketed_k2q_size_blocks(num_q_blocks: int, num_hea
     return 384
 
 
+def sm100_bwd_default_bucketed_k2q_size_blocks(num_q_blocks: int) -> int:
+    """Default query-group size of the 64-token backward CSR (csrc/bwd/sm100_blk64/bsa_bwd_sm100.py:21-24)."""
+    if num_q_blocks < 2048 or num_q_blocks >= 8192:
+        return 1088
+    return 1152
+
+
 # --------------------------------------------------------------------------------------------------
 # shared forward launcher
 # --------------------------------------------------------------------------------------------------
@@ -291,7 +298,9 @@ def bsa_attn_fwd(
     assert q.is_cuda and k.is_cuda and v.is_cuda, "inputs must be on CUDA device"
     assert q.device == k.device == v.device, "Q/K/V must be on the same CUDA device"
     assert q.dtype == k.dtype == v.dtype, "inputs must have the same dtype"
-    assert q.dtype == torch.bfloat16, "this engine computes in bfloat16"
+    assert q.dtype in (torch.float16, torch.bfloat16), "inputs must be float16 or bfloat16"
+    if q.dtype == torch.float16:
+        assert sparse_block_size == 128, "sparse_block_size=64 requires Q/K/V to all use bf16"
     q, k, v = [maybe_contiguous(t) for t in (q, k, v)]
     qb, kb, vb = (q, k, v) if layout == "bhsd" else (q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2))
     B, Hq, Sq, D = qb.shape
@@ -356,7 +365,8 @@ def bsa_attn_fwd(
     _launch_fwd(q=qb, k=kb, v=vb, out=out_b, lse=lse_buf, q2k_block_index=q2k_block_index,
                 q2k_block_nums=q2k_block_nums, block_sizes=block_sizes, bs_strides=bs_strides, blk=blk,
                 block_sparse_num=block_sparse_num if q2k_block_nums is None else 0, pack_gqa=packed,
-                splits=splits, softmax_scale=softmax_scale, dtype_code=_cabi.BSA_DTYPE_BF16)
+                splits=splits, softmax_scale=softmax_scale,
+                dtype_code=_cabi.BSA_DTYPE_F16 if q.dtype == torch.float16 else _cabi.BSA_DTYPE_BF16)
     return out, (lse_buf if return_lse_result else None)
 
 
@@ -576,13 +586,16 @@ def bsa_attn_bwd(
     *,
     sparse_block_size: int = 64,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """Backward of ``bsa_attn_fwd`` (reference bsa_attn_interface.py:3759-3996): BF16, MHA, D = 128,
-    128-token blocks.  dQ, dK and dV are accumulated in tensor memory in a fixed order without atomics,
-    so repeated calls are bit-identical.  ``block_sizes`` only expresses the physical KV tail here, as in
-    the reference (the tail is always masked)."""
+    """Backward of ``bsa_attn_fwd`` (reference bsa_attn_interface.py:3759-3996; the 64-token driver is
+    ``_bsa_attn_bwd_bucketed_k2q_csr`` :4022-4290): BF16, MHA, D = 128, 64- or 128-token blocks.  dQ, dK
+    and dV are accumulated in tensor memory in a fixed order without atomics, so repeated calls are
+    bit-identical.  ``block_sizes`` (rank 1 ``(num_kv_blocks,)`` or rank 2 ``(batch, num_kv_blocks)``)
+    masks the tail tokens of KV blocks exactly as the forward does; the physical KV tail is always masked.
+    The reference's 128-token backward ignores ``block_sizes``; with the full-block sizes its tests pass
+    the results are the same."""
     assert sparse_block_size in (64, 128), f"sparse_block_size must be 64 or 128, got {sparse_block_size}"
     assert layout in ("bhsd", "bshd"), f"layout must be 'bhsd' or 'bshd', got {layout!r}"
-    assert sparse_block_size == 128, "backward is built for sparse_block_size=128 only"
+    blk = sparse_block_size
     q, k, v, out, dout = [maybe_contiguous(t) for t in (q, k, v, out, dout)]
     if block_sizes is not None and block_sizes.numel() == 0:
         block_sizes = None
@@ -602,7 +615,11 @@ def bsa_attn_bwd(
     assert ob.shape == qb.shape and dob.shape == qb.shape
     assert lse.shape == (B, H, Sq)
     device = q.device
-    Nq, Nkv = _ceil_div(Sq, 128), _ceil_div(Sk, 128)
+    Nq, Nkv = _ceil_div(Sq, blk), _ceil_div(Sk, blk)
+    if block_sizes is not None:
+        assert block_sizes.dtype == torch.int32 and block_sizes.device == device
+        block_sizes = block_sizes.contiguous()
+    bs_strides = _block_size_strides(block_sizes, B, H, Nkv, (1, 2))
     assert q2k_block_index.dtype == torch.int32
     assert q2k_block_index.shape[:3] == (B, H, Nq), (
         f"q2k_block_index has shape {tuple(q2k_block_index.shape)}, expected (b={B}, h={H}, num_q_blocks={Nq}, "
@@ -619,7 +636,8 @@ def bsa_attn_bwd(
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(D)
     if bucket_size_blocks is None or bucket_size_blocks <= 0:
-        bucket_size_blocks = sm100_blk128_bwd_default_bucketed_k2q_size_blocks(Nq, H)
+        bucket_size_blocks = (sm100_blk128_bwd_default_bucketed_k2q_size_blocks(Nq, H) if blk == 128
+                              else sm100_bwd_default_bucketed_k2q_size_blocks(Nq))
 
     def _grad(buf, like):
         shape = like.shape
@@ -659,13 +677,15 @@ def bsa_attn_bwd(
     a.q2k_index = q2k_block_index.data_ptr()
     a.q2k_nums = _cabi.ptr(q2k_block_nums)
     a.csr_offsets, a.csr_indices = offsets.data_ptr(), indices.data_ptr()
+    a.block_sizes = _cabi.ptr(block_sizes)
+    a.bs_stride_b, a.bs_stride_h = bs_strides
     a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
     a.status = _cabi.status_buffer(device).data_ptr()
     a.do_stride, a.q_stride = _cabi.strides3(views["dout"]), _cabi.strides3(views["q"])
     a.k_stride, a.v_stride = _cabi.strides3(views["k"]), _cabi.strides3(views["v"])
     a.o_stride = _cabi.strides3(views["out"])
     a.dq_stride, a.dk_stride, a.dv_stride = (_cabi.strides3(outs[n]) for n in ("dq", "dk", "dv"))
-    a.blk = 128
+    a.blk = blk
     a.B, a.H, a.Sq, a.Sk, a.D = B, H, Sq, Sk, D
     a.cap = q2k_block_index.shape[-1]
     a.block_sparse_num = int(block_sparse_num) if q2k_block_nums is None else 0

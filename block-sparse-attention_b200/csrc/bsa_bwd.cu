@@ -45,6 +45,8 @@ struct BwdParams {
   const int32_t* __restrict__ q2k_nums;
   const int32_t* __restrict__ csr_offsets;
   const int32_t* __restrict__ csr_indices;
+  const int32_t* __restrict__ block_sizes;  // optional valid-token counts of the KV blocks
+  long long bs_stride_b, bs_stride_h;
   const float* __restrict__ lse_log2;  // [B,H,Nq*128]
   const float* __restrict__ delta;     // [B,H,Nq*128]
   __nv_bfloat16* dq;
@@ -102,6 +104,15 @@ bwd_preprocess_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* 
 // ------------------------------------------------------------------------------------------------
 // shared pieces of the two main kernels
 // ------------------------------------------------------------------------------------------------
+// Valid tokens of KV block j of (b, h): min(block_sizes[j], tokens physically left), 0 for ids out of range.
+template <int BLK>
+__device__ __forceinline__ int bwd_block_len(const BwdParams& p, int b, int h, int j) {
+  if (j < 0 || j >= p.Nkv) return 0;
+  int lim = min(BLK, p.Sk - j * BLK);
+  if (p.block_sizes) lim = min(lim, p.block_sizes[b * p.bs_stride_b + h * p.bs_stride_h + j]);
+  return max(lim, 0);
+}
+
 struct BwdSmem {
   static constexpr int kBarBytes = 256;  // 32 mbarriers
   static constexpr int kMisc = 16;
@@ -168,6 +179,10 @@ __device__ __forceinline__ void mma_ts_kmn(uint32_t d, uint32_t a_lo, uint32_t a
 constexpr int kDqStages = 5;
 constexpr int kDqSmem = 2 * kTile + kDqStages * kTile + BwdSmem::kBarBytes + BwdSmem::kMisc;
 
+// BLK = 64: the query tile has 64 rows (top half of the 128-row MMAs, lanes 64-127 idle) and one KV iteration
+// gathers two 64-token blocks into a 128-token tile (an odd count re-loads the last block as a masked phantom);
+// compute group g then owns exactly block g of the pair.
+template <int BLK>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
               const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const BwdParams p) {
@@ -220,16 +235,20 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   const uint32_t tdP = tmem + 256u, tdQ = tmem + 384u;
   const int num_work = p.B * p.H * p.Nq;
 
+  constexpr int kPerIt = 128 / BLK;               // KV blocks per 128-token iteration
+  constexpr uint32_t kQBytes = 2u * BLK * 128u;   // bytes of a Q (or dO) tile: two slabs of BLK rows
   auto row_count = [&](int w) {
     int c = p.q2k_nums ? p.q2k_nums[w] : p.fixed_count;
     return max(0, min(c, p.cap));
   };
+  auto iterations = [&](int count) { return (count + kPerIt - 1) / kPerIt; };
 
   if (warp == kBwdLoadWarp) {
     uint32_t r_cnt = 0, q_cnt = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
-      const int n = row_count(w);
+      const int cnt = row_count(w);
+      const int n = iterations(cnt);
       if (n == 0) continue;
       const int m = w % p.Nq;
       const int h = (w / p.Nq) % p.H;
@@ -239,14 +258,15 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (!ok) break;
       ++q_cnt;
       if (lane == 0) {
-        mbar_arrive_expect_tx(BAR(kQFull), 2 * kTile);
+        mbar_arrive_expect_tx(BAR(kQFull), 2 * kQBytes);
         for (int sl = 0; sl < 2; ++sl) {
-          tma_load_4d(smem_u32(sQ + sl * kSlab), &tm_q, BAR(kQFull), sl * 64, m * 128, h, b);
-          tma_load_4d(smem_u32(sdO + sl * kSlab), &tm_do, BAR(kQFull), sl * 64, m * 128, h, b);
+          tma_load_4d(smem_u32(sQ + sl * kSlab), &tm_q, BAR(kQFull), sl * 64, m * BLK, h, b);
+          tma_load_4d(smem_u32(sdO + sl * kSlab), &tm_do, BAR(kQFull), sl * 64, m * BLK, h, b);
         }
       }
       for (int j = 0; j < n && ok; ++j) {
-        const int blk = row[j];
+        const int blk0 = row[kPerIt * j];
+        const int blk1 = (BLK == 64 && 2 * j + 1 < cnt) ? row[2 * j + 1] : blk0;
         for (int which = 0; which < 2 && ok; ++which) {
           const uint32_t stage = r_cnt % NS, ph = (r_cnt / NS) & 1;
           ok = mbar_wait(BAR(kREmpty + stage), ph ^ 1, wctx, 401);
@@ -254,9 +274,11 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           if (lane == 0) {
             mbar_arrive_expect_tx(BAR(kRFull + stage), kTile);
             const CUtensorMap* tm = which ? &tm_v : &tm_k;
-            for (int sl = 0; sl < 2; ++sl)
-              tma_load_4d(smem_u32(sRing + stage * kTile + sl * kSlab), tm, BAR(kRFull + stage), sl * 64, blk * 128,
-                          h, b);
+            for (int sl = 0; sl < 2; ++sl) {
+              const uint32_t dst = smem_u32(sRing + stage * kTile + sl * kSlab);
+              tma_load_4d(dst, tm, BAR(kRFull + stage), sl * 64, blk0 * BLK, h, b);
+              if (BLK == 64) tma_load_4d(dst + 64 * 128, tm, BAR(kRFull + stage), sl * 64, blk1 * 64, h, b);
+            }
           }
           ++r_cnt;
         }
@@ -270,7 +292,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const uint64_t ring_k = desc_k_major(smem_u32(sRing)), ring_mn = desc_mn_major(smem_u32(sRing));
     PT_DECL
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
-      const int n = row_count(w);
+      const int n = iterations(row_count(w));
       if (n == 0) continue;
       PT_MARK(0)
       ok = mbar_wait(BAR(kQFull), q_cnt & 1, wctx, 410);
@@ -351,34 +373,39 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   } else if (warp < 8) {
     const int grp = warp >> 2;
     const int row = threadIdx.x & 127;
+    const bool row_active = (BLK == 128) || (row < 64);  // warp-uniform
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     uint32_t r_cnt = 0, s_cnt[2] = {0, 0}, dp_cnt = 0, fin_cnt = 0;
     bool ok = true;
     PT_DECL
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
-      const int n = row_count(w);
+      const int cnt = row_count(w);
+      const int n = iterations(cnt);
       const int m = w % p.Nq;
       const int h = (w / p.Nq) % p.H;
       const int b = w / (p.Nq * p.H);
-      const int seq = m * 128 + row;
+      const int seq = m * BLK + row;
       __nv_bfloat16* dq_row = p.dq + b * p.dq_stride[0] + h * p.dq_stride[1] + (long long)seq * p.dq_stride[2] + grp * 64;
       if (n == 0) {
-        if (seq < p.Sq) {
+        if (row_active && seq < p.Sq) {
 #pragma unroll
           for (int ch = 0; ch < 8; ++ch) reinterpret_cast<uint4*>(dq_row)[ch] = make_uint4(0, 0, 0, 0);
         }
         continue;
       }
-      const long long srow = ((long long)b * p.H + h) * ((long long)p.Nq * 128) + seq;
-      const float lse2 = p.lse_log2[srow];
-      const float dlt = p.delta[srow];
+      const long long srow = ((long long)b * p.H + h) * ((long long)p.Nq * BLK) + seq;
+      const float lse2 = row_active ? p.lse_log2[srow] : INFINITY;
+      const float dlt = row_active ? p.delta[srow] : 0.f;
       const int32_t* idx_row = p.q2k_index + (long long)w * p.cap;
       const uint32_t base = r_cnt;
       for (int j = 0; j < n && ok; ++j) {
-        // valid kv tokens of this block (only the last physical block can be short)
-        const int blk = idx_row[j];
-        int len = p.Sk - blk * 128;
-        len = (blk < 0 || blk >= p.Nkv) ? 0 : min(len, 128);
+        // valid kv tokens among this group's 64 columns of the 128-token tile
+        int len;
+        if (BLK == 128) {
+          len = bwd_block_len<128>(p, b, h, idx_row[j]) - grp * 64;
+        } else {
+          len = (2 * j + grp < cnt) ? bwd_block_len<64>(p, b, h, idx_row[2 * j + grp]) : 0;
+        }
         // ---- phase 1: P = exp2(S*scale - lse)
         PT_MARK(0)
         ok = mbar_wait(BAR(kSFull + (j & 1)), s_cnt[j & 1] & 1, wctx, 420);
@@ -386,6 +413,14 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         PT_MARK(1)
         ++s_cnt[j & 1];
         tc_fence_after();
+        if (!row_active) {  // idle half of a 64-row tile: barrier protocol only
+          ok = mbar_wait(BAR(kDpFull), dp_cnt & 1, wctx, 421);
+          if (!ok) break;
+          ++dp_cnt;
+          tc_fence_before();
+          mbar_arrive(BAR(kDsFull));
+          continue;
+        }
         float pr[64];
         {
           uint32_t* u = reinterpret_cast<uint32_t*>(pr);
@@ -396,9 +431,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         const float neg_l = -lse2;
 #pragma unroll
         for (int c = 0; c < 64; ++c) pr[c] = ex2_approx(fmaf(pr[c], p.scale_log2, neg_l));
-        if (len < 128) {
+        if (len < 64) {
 #pragma unroll
-          for (int c = 0; c < 64; ++c) pr[c] = (grp * 64 + c < len) ? pr[c] : 0.f;
+          for (int c = 0; c < 64; ++c) pr[c] = (c < len) ? pr[c] : 0.f;
         }
         // ---- phase 2: dS = P o (dP - delta) -> bf16 -> shared memory (the V_j slot, K-major, swizzled)
         PT_MARK(2)
@@ -437,12 +472,14 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       ++fin_cnt;
       tc_fence_after();
       uint32_t acc[64];
-      tmem_ld32(tdQ + lane_base + grp * 64, acc);
-      tmem_ld32(tdQ + lane_base + grp * 64 + 32, acc + 32);
-      tmem_wait_ld();
+      if (row_active) {
+        tmem_ld32(tdQ + lane_base + grp * 64, acc);
+        tmem_ld32(tdQ + lane_base + grp * 64 + 32, acc + 32);
+        tmem_wait_ld();
+      }
       tc_fence_before();
       mbar_arrive(BAR(kDqFree));
-      if (seq < p.Sq) store_row_half(dq_row, acc, p.softmax_scale);
+      if (row_active && seq < p.Sq) store_row_half(dq_row, acc, p.softmax_scale);
       PT_MARK(5)
     }
     if ((warp & 3) == 0) { PTB_FLUSH(grp * 8) }
@@ -463,6 +500,10 @@ constexpr int kDkvStages = 4;
 constexpr int kStatSlots = 4;
 constexpr int kDkvSmem = 2 * kTile + kDkvStages * kTile + kStatSlots * 1024 + BwdSmem::kBarBytes + BwdSmem::kMisc;
 
+// BLK = 64: the KV block has 64 tokens (top half of the 128-row MMAs, lanes 64-127 idle) and one iteration
+// covers two CSR entries: their 64-row Q / dO tiles form one 128-row ring tile, so compute group g owns
+// entry g of the pair (an odd total re-loads the last entry as a masked phantom).
+template <int BLK>
 __global__ void __launch_bounds__(kDkvThreads, 1)
 bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const BwdParams p) {
@@ -516,6 +557,9 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const uint32_t tS = tmem, tdP = tmem + 128u, tdV = tmem + 256u, tdK = tmem + 384u;
   const int num_work = p.B * p.H * p.Nkv;
 
+  constexpr int kPerIt = 128 / BLK;              // CSR entries per 128-row iteration
+  constexpr uint32_t kKvBytes = 2u * BLK * 128u;  // bytes of the K (or V) block: two slabs of BLK rows
+  auto iterations = [&](int entries) { return (entries + kPerIt - 1) / kPerIt; };
   // number of query tiles attending kv block nb of (b,h): the CSR rows of all query groups
   auto total_rows = [&](int bh, int nb) {
     int t = 0;
@@ -538,40 +582,62 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (!ok) break;
       ++kv_cnt;
       if (lane == 0) {
-        mbar_arrive_expect_tx(BAR(kKvFull), 2 * kTile);
+        mbar_arrive_expect_tx(BAR(kKvFull), 2 * kKvBytes);
         for (int sl = 0; sl < 2; ++sl) {
-          tma_load_4d(smem_u32(sK + sl * kSlab), &tm_k, BAR(kKvFull), sl * 64, nb * 128, h, b);
-          tma_load_4d(smem_u32(sV + sl * kSlab), &tm_v, BAR(kKvFull), sl * 64, nb * 128, h, b);
+          tma_load_4d(smem_u32(sK + sl * kSlab), &tm_k, BAR(kKvFull), sl * 64, nb * BLK, h, b);
+          tma_load_4d(smem_u32(sV + sl * kSlab), &tm_v, BAR(kKvFull), sl * 64, nb * BLK, h, b);
         }
       }
+      // one ring tile pair (Q, dO) for the query blocks qa (rows 0..BLK) and, with 64-token blocks, qb
+      auto load_pair = [&](int qa, int qb) -> bool {
+        for (int which = 0; which < 2; ++which) {
+          const uint32_t stage = r_cnt % NS, ph = (r_cnt / NS) & 1;
+          if (!mbar_wait(BAR(kREmpty + stage), ph ^ 1, wctx, 501)) return false;
+          if (lane == 0) {
+            const CUtensorMap* tm = which ? &tm_do : &tm_q;
+            mbar_arrive_expect_tx(BAR(kRFull + stage), kTile + (which ? 0 : 1024));
+            for (int sl = 0; sl < 2; ++sl) {
+              const uint32_t dst = smem_u32(sRing + stage * kTile + sl * kSlab);
+              tma_load_4d(dst, tm, BAR(kRFull + stage), sl * 64, qa * BLK, h, b);
+              if (BLK == 64) tma_load_4d(dst + 64 * 128, tm, BAR(kRFull + stage), sl * 64, qb * 64, h, b);
+            }
+            if (!which) {
+              // row statistics of the query rows travel with their Q tile
+              float* st = sStats + (tile_cnt % kStatSlots) * 256;
+              const long long plane = (long long)bh * ((long long)p.Nq * BLK);
+              if (BLK == 128) {
+                bulk_load_1d(smem_u32(st), p.lse_log2 + plane + (long long)qa * 128, 512, BAR(kRFull + stage));
+                bulk_load_1d(smem_u32(st + 128), p.delta + plane + (long long)qa * 128, 512, BAR(kRFull + stage));
+              } else {
+                bulk_load_1d(smem_u32(st), p.lse_log2 + plane + (long long)qa * 64, 256, BAR(kRFull + stage));
+                bulk_load_1d(smem_u32(st + 64), p.lse_log2 + plane + (long long)qb * 64, 256, BAR(kRFull + stage));
+                bulk_load_1d(smem_u32(st + 128), p.delta + plane + (long long)qa * 64, 256, BAR(kRFull + stage));
+                bulk_load_1d(smem_u32(st + 192), p.delta + plane + (long long)qb * 64, 256, BAR(kRFull + stage));
+              }
+            }
+          }
+          ++r_cnt;
+        }
+        ++tile_cnt;
+        return true;
+      };
+      int pending = -1;  // first entry of an unfinished pair (64-token blocks)
       for (int g = 0; g < p.G && ok; ++g) {
         const int32_t* off = p.csr_offsets + ((long long)bh * p.G + g) * (p.Nkv + 1);
         const int beg = off[nb], end = off[nb + 1];
         for (int e = beg; e < end && ok; ++e) {
           const int qi = p.csr_indices[(long long)bh * p.idx_cap + e];
-          for (int which = 0; which < 2 && ok; ++which) {
-            const uint32_t stage = r_cnt % NS, ph = (r_cnt / NS) & 1;
-            ok = mbar_wait(BAR(kREmpty + stage), ph ^ 1, wctx, 501);
-            if (!ok) break;
-            if (lane == 0) {
-              const CUtensorMap* tm = which ? &tm_do : &tm_q;
-              mbar_arrive_expect_tx(BAR(kRFull + stage), kTile + (which ? 0 : 1024));
-              for (int sl = 0; sl < 2; ++sl)
-                tma_load_4d(smem_u32(sRing + stage * kTile + sl * kSlab), tm, BAR(kRFull + stage), sl * 64, qi * 128,
-                            h, b);
-              if (!which) {
-                // row statistics of this query tile travel with its Q tile
-                float* st = sStats + (tile_cnt % kStatSlots) * 256;
-                const long long srow = (long long)bh * ((long long)p.Nq * 128) + (long long)qi * 128;
-                bulk_load_1d(smem_u32(st), p.lse_log2 + srow, 512, BAR(kRFull + stage));
-                bulk_load_1d(smem_u32(st + 128), p.delta + srow, 512, BAR(kRFull + stage));
-              }
-            }
-            ++r_cnt;
+          if (BLK == 128) {
+            ok = load_pair(qi, qi);
+          } else if (pending < 0) {
+            pending = qi;
+          } else {
+            ok = load_pair(pending, qi);
+            pending = -1;
           }
-          ++tile_cnt;
         }
       }
+      if (ok && pending >= 0) ok = load_pair(pending, pending);  // odd total: masked phantom second half
     }
   } else if (warp == kBwdMmaWarp || warp == kBwdMmaWarp + 1) {
     // Two issuing warps (tcgen05.mma issue stalls the issuing thread at the execution rate, so a single
@@ -589,7 +655,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
       const int nb = w % p.Nkv;
       const int bh = w / p.Nkv;
-      const int T = total_rows(bh, nb);
+      const int T = iterations(total_rows(bh, nb));
       if (T == 0) continue;
       ok = mbar_wait(BAR(kKvFull), kv_cnt & 1, wctx, 510);
       if (!ok) break;
@@ -690,6 +756,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   } else if (warp < 8) {
     const int grp = warp >> 2;
     const int row = threadIdx.x & 127;  // kv token inside the block = tensor-memory lane
+    const bool row_active = (BLK == 128) || (row < 64);  // warp-uniform
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     uint32_t s_cnt = 0, dp_cnt = 0, fin_cnt = 0, tile_cnt = 0, r_cnt = 0;
     bool ok = true;
@@ -698,11 +765,13 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const int nb = w % p.Nkv;
       const int bh = w / p.Nkv;
       const int h = bh % p.H, b = bh / p.H;
-      const int T = total_rows(bh, nb);
+      const int entries = total_rows(bh, nb);
+      const int T = iterations(entries);
       const uint32_t base = r_cnt;
       r_cnt += 2 * T;
-      const int kv = nb * 128 + row;
-      const bool kv_valid = kv < p.Sk;
+      const int kv = nb * BLK + row;
+      const bool kv_valid = row_active && kv < p.Sk;                   // this thread stores a dK / dV row
+      const bool kv_live = row < bwd_block_len<BLK>(p, b, h, nb);       // the token takes part in the softmax
       __nv_bfloat16* dk_row = p.dk + b * p.dk_stride[0] + h * p.dk_stride[1] + (long long)kv * p.dk_stride[2] + grp * 64;
       __nv_bfloat16* dv_row = p.dv + b * p.dv_stride[0] + h * p.dv_stride[1] + (long long)kv * p.dv_stride[2] + grp * 64;
       if (T == 0) {
@@ -725,6 +794,14 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (!ok) break;
         PT_MARK(1)
         ++s_cnt;
+        if (!row_active) {  // idle half of a 64-token block: barrier protocol only
+          mbar_arrive(BAR(kPFull));
+          ok = mbar_wait(BAR(kDpFull), dp_cnt & 1, wctx, 521);
+          if (!ok) break;
+          ++dp_cnt;
+          mbar_arrive(BAR(kDsFull));
+          continue;
+        }
         {
           // observe the arrival of this tile's row statistics directly (they were copied on the Q
           // stage's barrier); the phase cannot have advanced further: the stage is held until dK
@@ -748,7 +825,8 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           pr[c4 * 4 + 2] = ex2_approx(fmaf(pr[c4 * 4 + 2], p.scale_log2, -l.z));
           pr[c4 * 4 + 3] = ex2_approx(fmaf(pr[c4 * 4 + 3], p.scale_log2, -l.w));
         }
-        if (!kv_valid) {
+        // masked KV token, or the phantom second half of an odd pair
+        if (!kv_live || (BLK == 64 && grp == 1 && 2 * i + 1 >= entries)) {
 #pragma unroll
           for (int c = 0; c < 64; ++c) pr[c] = 0.f;
         }
@@ -798,13 +876,15 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       ++fin_cnt;
       tc_fence_after();
       uint32_t acc[64];
-      tmem_ld32(tdV + lane_base + grp * 64, acc);
-      tmem_ld32(tdV + lane_base + grp * 64 + 32, acc + 32);
-      tmem_wait_ld();
-      if (kv_valid) store_row_half(dv_row, acc, 1.0f);
-      tmem_ld32(tdK + lane_base + grp * 64, acc);
-      tmem_ld32(tdK + lane_base + grp * 64 + 32, acc + 32);
-      tmem_wait_ld();
+      if (row_active) {
+        tmem_ld32(tdV + lane_base + grp * 64, acc);
+        tmem_ld32(tdV + lane_base + grp * 64 + 32, acc + 32);
+        tmem_wait_ld();
+        if (kv_valid) store_row_half(dv_row, acc, 1.0f);
+        tmem_ld32(tdK + lane_base + grp * 64, acc);
+        tmem_ld32(tdK + lane_base + grp * 64 + 32, acc + 32);
+        tmem_wait_ld();
+      }
       tc_fence_before();
       mbar_arrive(BAR(kFree));
       if (kv_valid) store_row_half(dk_row, acc, p.softmax_scale);
@@ -845,7 +925,7 @@ extern "C" int64_t bsa_bwd_workspace_bytes(int32_t B, int32_t H, int32_t Sq, int
 
 extern "C" int bsa_bwd(const bsa_bwd_args* a, void* cuda_stream) {
   if (!a) return set_error(BSA_ERR_INVALID, "bsa_bwd: null args");
-  if (a->blk != 128) return set_error(BSA_ERR_UNSUPPORTED, "bsa_bwd: only 128-token blocks are built");
+  if (a->blk != 128 && a->blk != 64) return set_error(BSA_ERR_UNSUPPORTED, "bsa_bwd: block size %d not built (64 or 128)", a->blk);
   if (a->D != 128) return set_error(BSA_ERR_UNSUPPORTED, "bsa_bwd: head dimension %d not built (128 only)", a->D);
   if (a->B < 1 || a->H < 1 || a->Sq < 1 || a->Sk < 1) return set_error(BSA_ERR_INVALID, "bsa_bwd: non-positive extent");
   if (!a->dout || !a->q || !a->k || !a->v || !a->out || !a->lse || !a->dq || !a->dk || !a->dv || !a->q2k_index ||
@@ -864,14 +944,15 @@ extern "C" int bsa_bwd(const bsa_bwd_args* a, void* cuda_stream) {
   const int num_sms = bsa_num_sms(dev);
   if (num_sms <= 0) return set_error(BSA_ERR_CUDA, "bsa_bwd: cannot query the SM count");
 
-  const int Nq = (a->Sq + 127) / 128, Nkv = (a->Sk + 127) / 128;
-  const long long rows_pad = (long long)a->B * a->H * Nq * 128;
+  const int blk = a->blk;
+  const int Nq = (a->Sq + blk - 1) / blk, Nkv = (a->Sk + blk - 1) / blk;
+  const long long rows_pad = (long long)a->B * a->H * Nq * blk;
   float* lse_log2 = reinterpret_cast<float*>(a->workspace);
   float* delta = lse_log2 + rows_pad;
   bwd_preprocess_kernel<<<(unsigned)((rows_pad + 7) / 8), 256, 0, st>>>(
       reinterpret_cast<const __nv_bfloat16*>(a->out), reinterpret_cast<const __nv_bfloat16*>(a->dout), a->lse, lse_log2,
       delta, a->o_stride[0], a->o_stride[1], a->o_stride[2], a->do_stride[0], a->do_stride[1], a->do_stride[2], a->H,
-      a->Sq, Nq * 128, rows_pad);
+      a->Sq, Nq * blk, rows_pad);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "bwd preprocess launch: %s", cudaGetErrorString(e));
 
@@ -879,7 +960,7 @@ extern "C" int bsa_bwd(const bsa_bwd_args* a, void* cuda_stream) {
   {
     uint64_t qd[4] = {128, (uint64_t)a->Sq, (uint64_t)a->H, (uint64_t)a->B};
     uint64_t kd[4] = {128, (uint64_t)a->Sk, (uint64_t)a->H, (uint64_t)a->B};
-    uint32_t box[4] = {64, 128, 1, 1};
+    uint32_t box[4] = {64, (uint32_t)blk, 1, 1};
     auto strides = [](const int64_t* s, uint64_t* out) {
       out[0] = (uint64_t)s[2] * 2;
       out[1] = (uint64_t)s[1] * 2;
@@ -901,6 +982,9 @@ extern "C" int bsa_bwd(const bsa_bwd_args* a, void* cuda_stream) {
   p.q2k_nums = a->q2k_nums;
   p.csr_offsets = a->csr_offsets;
   p.csr_indices = a->csr_indices;
+  p.block_sizes = a->block_sizes;
+  p.bs_stride_b = a->bs_stride_b;
+  p.bs_stride_h = a->bs_stride_h;
   p.lse_log2 = lse_log2;
   p.delta = delta;
   p.dq = reinterpret_cast<__nv_bfloat16*>(a->dq);
@@ -926,17 +1010,19 @@ extern "C" int bsa_bwd(const bsa_bwd_args* a, void* cuda_stream) {
   p.softmax_scale = a->softmax_scale;
   p.scale_log2 = a->softmax_scale * kLog2e;
 
-  e = cudaFuncSetAttribute(bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmem);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDkvSmem);
+  auto* dq_kernel = blk == 128 ? bwd_dq_kernel<128> : bwd_dq_kernel<64>;
+  auto* dkv_kernel = blk == 128 ? bwd_dkv_kernel<128> : bwd_dkv_kernel<64>;
+  e = cudaFuncSetAttribute(dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmem);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDkvSmem);
   if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "bsa_bwd: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
   const long long work_q = (long long)a->B * a->H * Nq, work_kv = (long long)a->B * a->H * Nkv;
   if (work_q > 0x7fffffffLL || work_kv > 0x7fffffffLL) return set_error(BSA_ERR_UNSUPPORTED, "bsa_bwd: too many tiles");
   const int grid_q = (int)(work_q < num_sms ? work_q : num_sms);
   const int grid_kv = (int)(work_kv < num_sms ? work_kv : num_sms);
-  bwd_dq_kernel<<<grid_q, kBwdThreads, kDqSmem, st>>>(tq, tdo, tk, tv, p);
+  dq_kernel<<<grid_q, kBwdThreads, kDqSmem, st>>>(tq, tdo, tk, tv, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "bwd dQ launch: %s", cudaGetErrorString(e));
-  bwd_dkv_kernel<<<grid_kv, kDkvThreads, kDkvSmem, st>>>(tq, tdo, tk, tv, p);
+  dkv_kernel<<<grid_kv, kDkvThreads, kDkvSmem, st>>>(tq, tdo, tk, tv, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "bwd dK/dV launch: %s", cudaGetErrorString(e));
   return BSA_OK;

@@ -373,6 +373,12 @@ __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
+// {lo, hi} -> packed f16x2 with lo in bits [0,16)
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
 // four floats -> packed e4m3x4, element 0 in bits [0,8)
 __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
   uint16_t lo, hi;

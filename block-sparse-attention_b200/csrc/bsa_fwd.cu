@@ -25,6 +25,8 @@
 #include "bsa_common.cuh"
 #include "bsa_host.h"
 
+#include <type_traits>
+
 // Phase timers (development aid, see bsa_common.cuh): the 64-slot buffer of an unsplit launch travels in
 // the otherwise unused partial_lse pointer.
 #define PT_FLUSH(base) PT_FLUSH_TO(reinterpret_cast<unsigned long long*>(p.partial_lse), base)
@@ -48,6 +50,7 @@ struct FwdParams {
   int B, Hq, Hkv, G, Hidx, packed;
   int Sq, Sk, NqT, Nkv;
   int splits;
+  int f16;  // 16-bit inputs are IEEE half instead of bfloat16 (128-token blocks, unsplit only)
   int num_work;  // B * Hidx * NqT * splits
   float scale_log2;
 };
@@ -314,9 +317,9 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     // PV(i) -> QK(i+2) is program order of one thread, which is what the aliasing of P_s with S_s needs.
     setmaxnreg_dec<56>();
     const int s = warp - kMmaWarp;
-    constexpr uint32_t kFmt = FP8 ? 0u : 1u;  // e4m3 / bf16
-    constexpr uint32_t idesc_qk = umma_idesc(kFmt, kFmt, 0, 0, 128, 128);
-    constexpr uint32_t idesc_pv = umma_idesc(kFmt, kFmt, 0, 1, 128, 128);
+    const uint32_t kFmt = (FP8 || p.f16) ? 0u : 1u;  // e4m3 (kind::f8f6f4) or f16 (kind::f16) = 0, bf16 = 1
+    const uint32_t idesc_qk = umma_idesc(kFmt, kFmt, 0, 0, 128, 128);
+    const uint32_t idesc_pv = umma_idesc(kFmt, kFmt, 0, 1, 128, 128);
     uint32_t ring_pos = 0, q_cnt = 0, p_cnt = 0;  // ring_pos: tiles of this stream's ring consumed so far
     const uint32_t ring_depth = s ? (uint32_t)(NS - Cfg::kRing0) : (uint32_t)Cfg::kRing0;
     const uint32_t ring_first = s ? (uint32_t)Cfg::kRing0 : 0u;
@@ -675,6 +678,8 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           unpack2(s1, y2, y3);
           a0 = y0; a1 = y1; a2 = y2; a3 = y3;
         } else {
+          // the loop is instantiated once per 16-bit format so that the choice costs nothing per element
+          auto exp_store = [&](auto is_f16) {
           const uint64_t sc2 = pack2(p.scale_log2, p.scale_log2);
           const uint64_t nm2 = pack2(neg_m, neg_m);
           uint64_t s0 = pack2(0.f, 0.f), s1 = s0;
@@ -697,7 +702,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               }
               if (e & 1) s1 = fadd2(s1, pe);
               else s0 = fadd2(s0, pe);
-              pk[e] = pack_bf16x2(x0, x1);
+              pk[e] = decltype(is_f16)::value ? pack_f16x2(x0, x1) : pack_bf16x2(x0, x1);
             }
             if (c4 == 2) {
               // the first half of P_s (four MMA k steps) is released on its own barrier; waiting for its
@@ -712,6 +717,9 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           unpack2(s0, y0, y1);
           unpack2(s1, y2, y3);
           a0 = y0; a1 = y1; a2 = y2; a3 = y3;
+          };
+          if (p.f16) exp_store(std::true_type{});
+          else exp_store(std::false_type{});
         }
         l_sum += (a0 + a1) + (a2 + a3);
         PT_MARK(4)
@@ -803,10 +811,17 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
           for (int ch = 0; ch < 8; ++ch) {
             uint4 v;
-            v.x = pack_bf16x2(acc[ch * 8 + 0], acc[ch * 8 + 1]);
-            v.y = pack_bf16x2(acc[ch * 8 + 2], acc[ch * 8 + 3]);
-            v.z = pack_bf16x2(acc[ch * 8 + 4], acc[ch * 8 + 5]);
-            v.w = pack_bf16x2(acc[ch * 8 + 6], acc[ch * 8 + 7]);
+            if (p.f16) {
+              v.x = pack_f16x2(acc[ch * 8 + 0], acc[ch * 8 + 1]);
+              v.y = pack_f16x2(acc[ch * 8 + 2], acc[ch * 8 + 3]);
+              v.z = pack_f16x2(acc[ch * 8 + 4], acc[ch * 8 + 5]);
+              v.w = pack_f16x2(acc[ch * 8 + 6], acc[ch * 8 + 7]);
+            } else {
+              v.x = pack_bf16x2(acc[ch * 8 + 0], acc[ch * 8 + 1]);
+              v.y = pack_bf16x2(acc[ch * 8 + 2], acc[ch * 8 + 3]);
+              v.z = pack_bf16x2(acc[ch * 8 + 4], acc[ch * 8 + 5]);
+              v.w = pack_bf16x2(acc[ch * 8 + 6], acc[ch * 8 + 7]);
+            }
             *reinterpret_cast<uint4*>(slab + row * 128 + ((ch ^ (row & 7)) << 4)) = v;
           }
         }
@@ -871,8 +886,10 @@ extern "C" int bsa_fwd(const bsa_fwd_args* a, void* cuda_stream) {
   if (!a) return set_error(BSA_ERR_INVALID, "bsa_fwd: null args");
   if (a->blk != 64 && a->blk != 128) return set_error(BSA_ERR_INVALID, "bsa_fwd: blk must be 64 or 128");
   if (a->D != 128) return set_error(BSA_ERR_UNSUPPORTED, "bsa_fwd: head dimension %d not built (128 only)", a->D);
-  if (a->dtype != BSA_DTYPE_BF16 && a->dtype != BSA_DTYPE_E4M3)
+  if (a->dtype != BSA_DTYPE_BF16 && a->dtype != BSA_DTYPE_E4M3 && a->dtype != BSA_DTYPE_F16)
     return set_error(BSA_ERR_INVALID, "bsa_fwd: unknown dtype %d", a->dtype);
+  if (a->dtype == BSA_DTYPE_F16 && (a->blk != 128 || a->splits != 1))
+    return set_error(BSA_ERR_UNSUPPORTED, "bsa_fwd: float16 is built for unsplit 128-token blocks only");
   if (a->B < 1 || a->Hq < 1 || a->Hkv < 1 || a->Sq < 1 || a->Sk < 1)
     return set_error(BSA_ERR_INVALID, "bsa_fwd: non-positive extent");
   if (a->Hq % a->Hkv != 0) return set_error(BSA_ERR_INVALID, "bsa_fwd: Hq %% Hkv != 0");
@@ -923,6 +940,7 @@ extern "C" int bsa_fwd(const bsa_fwd_args* a, void* cuda_stream) {
   p.NqT = (int)((rows + a->blk - 1) / a->blk);
   p.Nkv = (a->Sk + a->blk - 1) / a->blk;
   p.splits = a->splits;
+  p.f16 = a->dtype == BSA_DTYPE_F16;
   const long long work = (long long)p.B * p.Hidx * p.NqT * p.splits;
   if (work > 0x7fffffffLL) return set_error(BSA_ERR_UNSUPPORTED, "bsa_fwd: more than 2^31 work items");
   p.num_work = (int)work;
@@ -931,7 +949,8 @@ extern "C" int bsa_fwd(const bsa_fwd_args* a, void* cuda_stream) {
   // tensor maps.  Q and O: 5-D (D, G, S, Hkv, B) so that a packed-GQA tile (blk/G sequence positions x G
   // heads) is one box; K and V: 4-D (D, S, Hkv, B).
   const int elt = fp8 ? 1 : 2;
-  const CUtensorMapDataType dt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const CUtensorMapDataType dt16 = a->dtype == BSA_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  const CUtensorMapDataType dt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : dt16;
   const uint32_t inner = 128 / elt;  // elements per 128-byte swizzle row
   CUtensorMap tq, tk, tv, to;
   {
@@ -945,7 +964,7 @@ extern "C" int bsa_fwd(const bsa_fwd_args* a, void* cuda_stream) {
       uint64_t ostr[4] = {(uint64_t)a->o_stride[1] * 2, (uint64_t)a->o_stride[2] * 2,
                           (uint64_t)a->o_stride[1] * G * 2, (uint64_t)a->o_stride[0] * 2};
       uint32_t obox[5] = {64, packed ? (uint32_t)G : 1u, (uint32_t)(packed ? a->blk / G : a->blk), 1, 1};
-      rc = make_tensor_map(&to, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 5, a->out, dims, ostr, obox, "out");
+      rc = make_tensor_map(&to, dt16, 5, a->out, dims, ostr, obox, "out");
       if (rc) return rc;
     } else {
       to = tq;

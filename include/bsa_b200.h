@@ -23,7 +23,7 @@ extern "C" {
 
 #define BSA_B200_ABI_VERSION 1
 
-enum bsa_dtype { BSA_DTYPE_BF16 = 0, BSA_DTYPE_E4M3 = 1 };
+enum bsa_dtype { BSA_DTYPE_BF16 = 0, BSA_DTYPE_E4M3 = 1, BSA_DTYPE_F16 = 2 /* unsplit 128-token blocks only */ };
 
 /* Error codes returned by the entry points (negative). */
 enum bsa_error {
@@ -192,10 +192,15 @@ int bsa_build_k2q_csr(const int32_t* q2k_index, const int32_t* q2k_nums, int32_t
                       void* cuda_stream);
 
 /*
- * Backward pass, BF16, MHA, D = 128, 128-token blocks: dQ, dK, dV from dO, Q, K, V, O, LSE.
+ * Backward pass, BF16, MHA, D = 128, blk = 128 or 64 tokens: dQ, dK, dV from dO, Q, K, V, O, LSE.
  * Replaces the preprocess / main / postprocess callables of
- * csrc/bwd/sm100_blk128/bsa_bwd_sm100.py:2178-2385 (preprocess csrc/bwd/bsa_bwd_preprocess.py,
- * postprocess csrc/bwd/bsa_bwd_postprocess.py).
+ * csrc/bwd/sm100_blk128/bsa_bwd_sm100.py:2178-2385 (blk128) and of the blk64 driver
+ * bsa_attn_interface.py:4022-4290 over csrc/bwd/sm100_blk64/bsa_bwd_sm100.py (preprocess
+ * csrc/bwd/bsa_bwd_preprocess.py, postprocess csrc/bwd/bsa_bwd_postprocess.py).
+ *   block_sizes: NULL, or int32 valid-token counts of the KV blocks with element strides
+ *   (bs_stride_b, bs_stride_h, 1); tokens beyond a block's count get no probability and zero dK / dV,
+ *   exactly as the forward masks them (the reference's blk128 backward ignores block_sizes, its blk64
+ *   backward honours them; here both do);
  *   csr_offsets / csr_indices as produced by bsa_build_k2q_csr with the same q2k metadata;
  *   workspace: bsa_bwd_workspace_bytes(...) bytes of device memory, contents unspecified on entry.
  * dQ is accumulated without atomics and in a fixed order, so repeated calls are bit-identical.
@@ -214,6 +219,7 @@ typedef struct bsa_bwd_args {
   const int32_t* q2k_nums;
   const int32_t* csr_offsets;
   const int32_t* csr_indices;
+  const int32_t* block_sizes;
   void* workspace;
   int32_t* status;
   int64_t workspace_bytes;
@@ -225,6 +231,8 @@ typedef struct bsa_bwd_args {
   int64_t dq_stride[3];
   int64_t dk_stride[3];
   int64_t dv_stride[3];
+  int64_t bs_stride_b;
+  int64_t bs_stride_h;
   int32_t blk;
   int32_t B, H, Sq, Sk, D;
   int32_t cap;

@@ -222,10 +222,12 @@ def backward_dense(q, k, v, dout, attn_bias, softmax_scale, upcast=True):
     return out.detach().to(dout.dtype), lse.detach().float(), q_r.grad.detach(), k_r.grad.detach(), v_r.grad.detach()
 
 
-def backward_gathered(q, k, v, dout, index, count, nums=None, scale=None, blk=128, heads=None, batches=None):
+def backward_gathered(q, k, v, dout, index, count, nums=None, scale=None, blk=128, heads=None, batches=None,
+                      sizes=None):
     """Gathered-form backward for large shapes (MHA): per query block, autograd through the softmax over
     exactly the selected tokens; gradients scattered back.  Same math as ``backward_dense`` (the dense
-    bias only removes the unselected tokens), so it is validated against it on small cases."""
+    bias only removes the unselected tokens), so it is validated against it on small cases.  ``sizes``
+    (rank 1/2/3) are the valid-token counts of the KV blocks, as in ``attention_gathered``."""
     B, H, Sq, D = q.shape
     Sk = k.shape[2]
     scale = D ** -0.5 if scale is None else scale
@@ -242,7 +244,12 @@ def backward_gathered(q, k, v, dout, index, count, nums=None, scale=None, blk=12
                 s, e = m * blk, min((m + 1) * blk, Sq)
                 if n == 0 or s >= Sq:
                     continue
-                toks = torch.cat([(int(index[b, h, m, i]) * blk + off) for i in range(n)])
+                parts = []
+                for i in range(n):
+                    j = int(index[b, h, m, i])
+                    ext = blk if sizes is None else max(0, min(blk, _extent(sizes, b, h, j)))
+                    parts.append(j * blk + off[:ext])
+                toks = torch.cat(parts)
                 toks = toks[toks < Sk]
                 if toks.numel() == 0:
                     continue

@@ -190,6 +190,22 @@ def main():
                         dout=bf16_bits(do), index=index.numpy(), out=o.float().numpy(), lse=lse.numpy(),
                         dq=dq.numpy(), dk=dk.numpy(), dv=dv.numpy())
 
+    # ---------------------------------------------------------------- G2. backward, 64-token blocks, block_sizes
+    g = torch.Generator().manual_seed(22)
+    B, H, Sq, Sk = 1, 2, 192, 300
+    q, do = (rand_bf16(g, B, H, Sq, 128) for _ in range(2))
+    k, v = (rand_bf16(g, B, H, Sk, 128) for _ in range(2))
+    nq, nk = 3, 5
+    index = torch.stack([torch.randperm(nk, generator=g) for _ in range(B * H * nq)]).int().reshape(B, H, nq, nk)
+    nums = torch.tensor([[[3, 1, 4], [5, 2, 1]]], dtype=torch.int32)
+    sizes = torch.randint(1, 65, (nk,), generator=g, dtype=torch.int32)
+    sizes[-1].clamp_(max=Sk - (nk - 1) * 64)
+    bias = tff.block_sparse_to_attn_bias(index, 0, sizes, Sq, Sk, 64, 64, q2k_block_nums=nums)
+    o, lse, dq, dk, dv = tfb._torch_ref_bwd(q, k, v, do, bias, 1.0 / math.sqrt(128), upcast=True)
+    np.savez_compressed(os.path.join(HERE, "bwd_blk64_sizes.npz"), q=bf16_bits(q), k=bf16_bits(k), v=bf16_bits(v),
+                        dout=bf16_bits(do), index=index.numpy(), nums=nums.numpy(), sizes=sizes.numpy(),
+                        out=o.float().numpy(), lse=lse.numpy(), dq=dq.numpy(), dk=dk.numpy(), dv=dv.numpy())
+
     # ---------------------------------------------------------------- H. split policy table
     counts = [1, 2, 31, 255, 256, 449, 450, 899, 900, 2048]
     table = [ref_iface._sm100_blk64_kv_splits_from_count(c) for c in counts]

@@ -1,5 +1,5 @@
-"""GPU parity of the backward pass (BF16, MHA, D = 128, 128-token blocks) against torch autograd on the
-CPU oracle.  Tolerance per gradient is the reference's: 3 * |bf16 autograd - fp32 autograd|max +
+"""GPU parity of the backward pass (BF16, MHA, D = 128, 128- and 64-token blocks) against torch autograd on
+the CPU oracle.  Tolerance per gradient is the reference's: 3 * |bf16 autograd - fp32 autograd|max +
 3 * bf16 round-trip eps + 5e-3 (tests/test_flash_bwd.py:53-61)."""
 import math
 
@@ -12,19 +12,22 @@ from oracle import bsa_oracle as orc
 pytestmark = pytest.mark.gpu
 
 
-def _run(q, k, v, do, index, count, nums=None, scale=None, layout="bhsd", bucket=None, bufs=False):
+def _run(q, k, v, do, index, count, nums=None, scale=None, layout="bhsd", bucket=None, bufs=False, blk=128,
+         sizes=None):
     from block_sparse_attention import bsa_attn_bwd, bsa_attn_fwd
     c = lambda t: None if t is None else t.cuda()
-    qc, kc, vc, doc, ic, nc = c(q), c(k), c(v), c(do), c(index), c(nums)
+    qc, kc, vc, doc, ic, nc, sc = c(q), c(k), c(v), c(do), c(index), c(nums), c(sizes)
     if layout == "bshd":
         qc, kc, vc, doc = (t.transpose(1, 2).contiguous() for t in (qc, kc, vc, doc))
-    out, lse = bsa_attn_fwd(qc, kc, vc, ic, count, q2k_block_nums=nc, softmax_scale=scale, return_lse=True,
-                            layout=layout, sparse_block_size=128)
+    out, lse = bsa_attn_fwd(qc, kc, vc, ic, count, block_sizes=sc, q2k_block_nums=nc, softmax_scale=scale,
+                            return_lse=True, layout=layout, sparse_block_size=blk,
+                            allow_empty_block_nums=True)
     kw = {}
     if bufs:
         kw = dict(dq=torch.full_like(qc, 7.0), dk=torch.full_like(kc, 7.0), dv=torch.full_like(vc, 7.0))
-    dq, dk, dv = bsa_attn_bwd(doc, qc, kc, vc, out, lse, ic, count, q2k_block_nums=nc, softmax_scale=scale,
-                              bucket_size_blocks=bucket, layout=layout, sparse_block_size=128, **kw)
+    dq, dk, dv = bsa_attn_bwd(doc, qc, kc, vc, out, lse, ic, count, block_sizes=sc, q2k_block_nums=nc,
+                              softmax_scale=scale, bucket_size_blocks=bucket, layout=layout, sparse_block_size=blk,
+                              **kw)
     if bufs:
         assert dq is kw["dq"] and dk is kw["dk"] and dv is kw["dv"]
     if layout == "bshd":
@@ -66,11 +69,11 @@ def test_golden_backward():
     _check(got, q, k, v, do, bias, 1 / math.sqrt(128))
 
 
-def _case(seed, B, H, Sq, Sk, counts, poison=True):
+def _case(seed, B, H, Sq, Sk, counts, poison=True, blk=128):
     gen = torch.Generator().manual_seed(seed)
     q, do = (torch.randn(B, H, Sq, 128, generator=gen).bfloat16() for _ in range(2))
     k, v = (torch.randn(B, H, Sk, 128, generator=gen).bfloat16() for _ in range(2))
-    Nq, Nkv = math.ceil(Sq / 128), math.ceil(Sk / 128)
+    Nq, Nkv = math.ceil(Sq / blk), math.ceil(Sk / blk)
     index = torch.zeros(B, H, Nq, Nkv, dtype=torch.int32)
     nums = torch.zeros(B, H, Nq, dtype=torch.int32)
     i = 0
@@ -129,6 +132,76 @@ def test_repeat_calls_are_bit_identical_many_tiles():
         assert (got[1, 1] - ref[1, 1]).abs().max().item() < 6e-2
 
 
+# --------------------------------------------------------------------------------------------------
+# 64-token blocks (shapes of the reference's tests/test_flash_bwd.py:611-668 plus ragged ones)
+# --------------------------------------------------------------------------------------------------
+def test_golden_backward_64_token_blocks_with_block_sizes():
+    g = load_golden("bwd_blk64_sizes.npz")
+    q, k, v, do = (bf16_from_bits(g[n]) for n in ("q", "k", "v", "dout"))
+    index, nums, sizes = (torch.from_numpy(g[n]) for n in ("index", "nums", "sizes"))
+    got = _run(q, k, v, do, index, 0, nums=nums, blk=64, sizes=sizes)
+    for name, t in zip(("dq", "dk", "dv"), got):
+        assert (t - torch.from_numpy(g[name])).abs().max().item() < 3e-2, name
+    bias = orc.block_sparse_to_attn_bias(index, 0, sizes, q.shape[2], k.shape[2], 64, 64, q2k_block_nums=nums)
+    _check(got, q, k, v, do, bias, 1 / math.sqrt(128))
+    # tokens beyond a block's valid size take no part: exact zero dK / dV
+    for j, n in enumerate(sizes.tolist()):
+        lo, hi = j * 64 + n, min((j + 1) * 64, k.shape[2])
+        assert (got[1][:, :, lo:hi] == 0).all() and (got[2][:, :, lo:hi] == 0).all()
+
+
+@pytest.mark.parametrize("variable", [False, True])
+@pytest.mark.parametrize("Sq,Sk", [(64, 256), (128, 512), (256, 1024), (512, 512), (1024, 1024), (300, 700)])
+def test_64_token_blocks_sparse(Sq, Sk, variable):
+    Nkv = math.ceil(Sk / 64)
+    counts = [3, 1, 4, 0, 2, 5, Nkv] if variable else [min(3, Nkv)]
+    q, k, v, do, index, nums = _case(5, 2 if Sk <= 512 else 1, 4, Sq, Sk, counts, poison=variable, blk=64)
+    sizes = torch.full((Nkv,), 64, dtype=torch.int32)
+    sizes[-1] = Sk - (Nkv - 1) * 64
+    if variable:
+        got = _run(q, k, v, do, index, 0, nums=nums, blk=64, sizes=sizes)
+        bias = orc.block_sparse_to_attn_bias(index.clamp(max=Nkv - 1), 0, sizes, Sq, Sk, 64, 64, q2k_block_nums=nums)
+    else:
+        got = _run(q, k, v, do, index, counts[0], blk=64)  # no block_sizes: the tail is masked regardless
+        bias = orc.block_sparse_to_attn_bias(index, counts[0], sizes, Sq, Sk, 64, 64)
+    _check(got, q, k, v, do, bias, 1 / math.sqrt(128))
+
+
+def test_64_token_blocks_grouping_layout_and_per_batch_sizes():
+    q, k, v, do, index, nums = _case(6, 2, 2, 512, 768, [5, 2, 7, 3], poison=False, blk=64)
+    gen = torch.Generator().manual_seed(60)
+    sizes = torch.randint(1, 65, (2, 12), generator=gen, dtype=torch.int32)  # rank 2: (batch, kv blocks)
+    a = _run(q, k, v, do, index, 0, nums=nums, blk=64, sizes=sizes, bucket=2)  # four query groups
+    b = _run(q, k, v, do, index, 0, nums=nums, blk=64, sizes=sizes, bucket=512, layout="bshd", bufs=True)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y), "grouping / layout must not change the result"
+    for bi in range(2):
+        bias = orc.block_sparse_to_attn_bias(index[bi:bi + 1], 0, sizes[bi], 512, 768, 64, 64,
+                                             q2k_block_nums=nums[bi:bi + 1])
+        _check(tuple(t[bi:bi + 1] for t in a), q[bi:bi + 1], k[bi:bi + 1], v[bi:bi + 1], do[bi:bi + 1], bias,
+               1 / math.sqrt(128))
+
+
+def test_64_token_blocks_many_tiles_repeatable():
+    """more work items than SMs in both kernels, odd and even entry counts per KV block."""
+    q, k, v, do, index, nums = _case(8, 2, 4, 2048, 2048, [5, 3, 8, 1, 0, 6, 9], blk=64)
+    a = _run(q, k, v, do, index, 0, nums=nums, blk=64)
+    b = _run(q, k, v, do, index, 0, nums=nums, blk=64)
+    for x, y in zip(a, b):
+        assert torch.equal(x, y)
+    gq, gk, gv = orc.backward_gathered(q, k, v, do, index.clamp(max=31), 0, nums=nums, blk=64, heads=[2], batches=[1])
+    for got, ref in zip(a, (gq, gk, gv)):
+        assert (got[1, 2] - ref[1, 2]).abs().max().item() < 6e-2
+
+
+def test_128_token_blocks_honour_block_sizes_like_the_forward():
+    q, k, v, do, index, nums = _case(9, 1, 2, 384, 512, [2, 3, 1], poison=False)
+    sizes = torch.tensor([128, 40, 97, 1], dtype=torch.int32)
+    got = _run(q, k, v, do, index, 0, nums=nums, sizes=sizes)
+    bias = orc.block_sparse_to_attn_bias(index, 0, sizes, 384, 512, q2k_block_nums=nums)
+    _check(got, q, k, v, do, bias, 1 / math.sqrt(128))
+
+
 def test_argument_errors():
     from block_sparse_attention import bsa_attn_bwd
     x = torch.zeros(1, 2, 128, 128, device="cuda").bfloat16()
@@ -150,6 +223,18 @@ def test_autograd_function_matches_oracle_gradients():
     out.backward(do.cuda())
     bias = orc.block_sparse_to_attn_bias(index, 0, torch.full((5,), 128, dtype=torch.int32), 512, 640,
                                          q2k_block_nums=nums)
+    _check(tuple(t.grad.float().cpu() for t in (qc, kc, vc)), q, k, v, do, bias, 1 / math.sqrt(128))
+
+
+def test_autograd_function_64_token_blocks():
+    from block_sparse_attention import block_sparse_attention
+    q, k, v, do, index, nums = _case(12, 1, 2, 256, 320, [3, 1, 4, 2], poison=False, blk=64)
+    sizes = torch.tensor([64, 10, 64, 33, 64], dtype=torch.int32)
+    qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+    out = block_sparse_attention(qc, kc, vc, index.cuda(), 0, q2k_block_nums=nums.cuda(), sparse_block_size=64,
+                                 block_sizes=sizes.cuda())
+    out.backward(do.cuda())
+    bias = orc.block_sparse_to_attn_bias(index, 0, sizes, 256, 320, 64, 64, q2k_block_nums=nums)
     _check(tuple(t.grad.float().cpu() for t in (qc, kc, vc)), q, k, v, do, bias, 1 / math.sqrt(128))
 
 

@@ -306,3 +306,17 @@ def test_batch_stride_beyond_2_to_the_31_elements():
     out, lse = _fwd(q.cuda(), k_view, v.cuda(), index.cuda(), 2, return_lse=True, sparse_block_size=128)
     ref_out, ref_lse = orc.attention_gathered(q, k, v, index, 2)
     _check(out, lse, ref_out, ref_lse, q, k, v)
+
+
+def test_float16_inputs_128_token_blocks():
+    """the 128-block forward also takes IEEE half inputs (bsa_attn_interface.py:3527: 'inputs must be
+    float16 or bfloat16'); 64-token blocks stay bf16-only like the reference (:2360-2363)."""
+    q, k, v, index, nums, sizes = _random_case(37, 1, 4, 2, 384, 640, 128, [3, 5, 0, 1], sizes_rank=1)
+    qh, kh, vh = q.half(), k.half(), v.half()
+    out, lse = _fwd(qh.cuda(), kh.cuda(), vh.cuda(), index.cuda(), 0, block_sizes=sizes.cuda(),
+                    q2k_block_nums=nums.cuda(), return_lse=True, sparse_block_size=128, pack_gqa=False)
+    assert out.dtype == torch.float16
+    ref_out, ref_lse = orc.attention_gathered(qh, kh, vh, index, 0, nums=nums, sizes=sizes)
+    _check(out, lse, ref_out, ref_lse, qh, kh, vh)
+    with pytest.raises(AssertionError):
+        _fwd(qh.cuda()[:, :2], kh.cuda(), vh.cuda(), index.cuda()[:, :2, :, :4].contiguous(), 2, sparse_block_size=64)

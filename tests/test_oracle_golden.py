@@ -140,6 +140,21 @@ def test_backward_matches_reference():
         assert torch.allclose(got, torch.from_numpy(g[name]), atol=2e-4, rtol=1e-4), name
 
 
+def test_backward_64_token_blocks_with_block_sizes_matches_reference():
+    g = load_golden("bwd_blk64_sizes.npz")
+    q, k, v, do = (bf16_from_bits(g[n]) for n in ("q", "k", "v", "dout"))
+    index, nums, sizes = (torch.from_numpy(g[n]) for n in ("index", "nums", "sizes"))
+    Sq, Sk = q.shape[2], k.shape[2]
+    bias = orc.block_sparse_to_attn_bias(index, 0, sizes, Sq, Sk, 64, 64, q2k_block_nums=nums)
+    scale = 1.0 / math.sqrt(128)
+    o, lse, dq, dk, dv = orc.backward_dense(q, k, v, do, bias, scale)
+    for got, name in ((dq, "dq"), (dk, "dk"), (dv, "dv"), (lse, "lse")):
+        assert torch.allclose(got, torch.from_numpy(g[name]), atol=1e-5, rtol=1e-5), name
+    gq, gk, gv = orc.backward_gathered(q, k, v, do, index, 0, nums=nums, scale=scale, blk=64, sizes=sizes)
+    for got, name in ((gq, "dq"), (gk, "dk"), (gv, "dv")):
+        assert torch.allclose(got, torch.from_numpy(g[name]), atol=2e-4, rtol=1e-4), name
+
+
 def test_split_policy_matches_reference():
     g = load_golden("policy_blk64_splits.npz")
     for c, s in zip(g["counts"].tolist(), g["splits"].tolist()):
