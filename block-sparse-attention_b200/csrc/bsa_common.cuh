@@ -138,6 +138,49 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   return __all_sync(0xffffffffu, done);
 }
 
+// Non-blocking test of a phase (mbarrier.test_wait never suspends the thread).
+__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Same contract as mbar_wait, but polls instead of letting the hardware suspend the thread: the wake-up
+// after a suspended try_wait costs a few hundred clocks, which a role on the critical path (an MMA
+// issuer) cannot hide.  The abort flag and the time limit are checked every 64 polls.
+__device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int site) {
+  bool done = mbar_test_wait(bar, parity);
+  if (!done) {
+    const uint64_t t0 = globaltimer_ns();
+    uint32_t polls = 0;
+    for (;;) {
+      if (mbar_test_wait(bar, parity)) {
+        done = true;
+        break;
+      }
+      if ((++polls & 63u) != 0) continue;
+      if (*ctx.abort_flag) break;
+      if (globaltimer_ns() - t0 > BSA_WAIT_LIMIT_NS) {
+        *ctx.abort_flag = 1;
+        if (atomicCAS(ctx.status, 0, (int)kStatusWaitTimeout) == 0) {
+          ctx.status[1] = (int)blockIdx.x;
+          ctx.status[2] = site;
+          ctx.status[3] = (int)threadIdx.x;
+        }
+        __threadfence();
+        break;
+      }
+    }
+  }
+  return __all_sync(0xffffffffu, done);
+}
+
 // Rendezvous of `count` threads through an mbarrier initialised with that count: arrive, then a
 // bounded wait.  Unlike bar.sync it cannot strand the threads that are already waiting when another
 // role aborts.  `phase_cnt` counts the uses of this barrier by the calling thread.
@@ -145,6 +188,16 @@ __device__ __forceinline__ bool mbar_rendezvous(uint32_t bar, uint32_t& phase_cn
                                                 int site) {
   mbar_arrive(bar);
   const bool ok = mbar_wait(bar, phase_cnt & 1, ctx, site);
+  ++phase_cnt;
+  return ok;
+}
+
+// Rendezvous for short, rare meeting points (a tile epilogue): polls, so the last arrival is seen within
+// tens of clocks instead of the few hundred a suspended wait needs to wake up.
+__device__ __forceinline__ bool mbar_rendezvous_poll(uint32_t bar, uint32_t& phase_cnt, const WaitCtx& ctx,
+                                                     int site) {
+  mbar_arrive(bar);
+  const bool ok = mbar_wait_poll(bar, phase_cnt & 1, ctx, site);
   ++phase_cnt;
   return ok;
 }

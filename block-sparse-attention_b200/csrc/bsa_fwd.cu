@@ -30,6 +30,17 @@
 // Phase timers (development aid, see bsa_common.cuh): the 64-slot buffer of an unsplit launch travels in
 // the otherwise unused partial_lse pointer.
 #define PT_FLUSH(base) PT_FLUSH_TO(reinterpret_cast<unsigned long long*>(p.partial_lse), base)
+#ifdef BSA_PHASE_TRACE
+// development aid: CTA 0 records clock64() of selected events of its first iterations behind the 64 counters
+#define PT_TRACE(stream, slot) if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && pt_trace_n[stream] < 256) { \
+    reinterpret_cast<unsigned long long*>(p.partial_lse)[64 + (stream) * 1024 + pt_trace_n[stream] * 4 + (slot)] = clock64(); }
+#define PT_TRACE_NEXT(stream) ++pt_trace_n[stream];
+#define PT_TRACE_DECL int pt_trace_n[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#else
+#define PT_TRACE(stream, slot)
+#define PT_TRACE_NEXT(stream)
+#define PT_TRACE_DECL
+#endif
 
 namespace bsa {
 
@@ -62,10 +73,10 @@ struct FwdParams {
 #define BSA_EX2_EMU8 0
 #endif
 
-constexpr int kThreads = 384;  // warp 11 only gives its registers away
+constexpr int kThreads = 384;
 constexpr int kSoftmaxThreads = 256;
 constexpr int kMmaWarp = 8;
-constexpr int kLoadWarp = 10;  // warps 8 and 9 issue the MMAs of stream 0 and 1
+constexpr int kLoadWarp = 10;  // warps 8 and 9 issue the MMAs of stream 0 and 1, warps 10 and 11 load their K/V tiles
 
 
 template <bool FP8>
@@ -82,8 +93,8 @@ struct FwdCfg {
   static constexpr int kMmaK = FP8 ? 32 : 16;
   static constexpr int kKSteps = 128 / kMmaK;
   static constexpr int kPColsPerStep = FP8 ? 8 : 8;  // tensor-memory columns of P per MMA k step
-  // smem: Q | O | KV stages | 32 barriers | stats [2][128] float2 | tmem base, abort flag
-  static constexpr int kSmemBytes = kTileBytes + kOBytes + kStages * kTileBytes + 256 + 2048 + 16;
+  // smem: Q | O | KV stages | 32 barriers | stats [2][128] float2 | tmem base, abort flag | 2 turn barriers
+  static constexpr int kSmemBytes = kTileBytes + kOBytes + kStages * kTileBytes + 256 + 2048 + 16 + 16;
 };
 
 struct WorkItem {
@@ -168,11 +179,12 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   const uint32_t bar_base = smem_u32(bars);
   auto BAR = [&](int i) { return bar_base + (uint32_t)i * 8u; };
   constexpr int kQFull = 0, kQEmpty = 1, kKvFull = 2, kKvEmpty = 2 + NS, kSFull = 2 + 2 * NS,
-                kPFull = kSFull + 2, kOFinal = kPFull + 2, kEpiA = kOFinal + 2, kEpiB = kEpiA + 1,
-                kGrpA = kEpiB + 1, kGrpB = kGrpA + 2, kPHalf = kGrpB + 2, kNumBars = kPHalf + 2;
+                kPFull = kSFull + 2, kOFinal = kPFull + 2, kEpiA = kOFinal + 2, kGrpB = kEpiA + 1,
+                kPHalf = kGrpB + 2, kNumBars = kPHalf + 2;
   float2 (*s_stats)[128] = reinterpret_cast<float2 (*)[128]>(bars + 32);  // [2][128] (max, sum)
   uint32_t& s_tmem_base = *reinterpret_cast<uint32_t*>(bars + 32 + 256);
   volatile int& s_abort = *reinterpret_cast<volatile int*>(bars + 32 + 256 + 1);
+  const uint32_t turn_base = smem_u32(bars + 32 + 256 + 2);  // two more barriers: the issuers' turn tokens
   if ((smem_u32(smem_raw) & 1023u) != 0) {  // uniform over the CTA: nothing has been set up yet
     if (threadIdx.x == 0 && atomicCAS(p.status, 0, (int)kStatusBadIndex) == 0) p.status[2] = 999;
     return;
@@ -196,14 +208,12 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       mbar_init(BAR(kPFull + s), 128);
       mbar_init(BAR(kPHalf + s), 128);
     }
+    mbar_init(turn_base, 1);
+    mbar_init(turn_base + 8, 1);
     mbar_init(BAR(kOFinal), 1);  // one per stream: a stream without work in a tile neither arrives nor is waited for
     mbar_init(BAR(kOFinal + 1), 1);
     mbar_init(BAR(kEpiA), kSoftmaxThreads);
-    mbar_init(BAR(kEpiB), kSoftmaxThreads);
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(BAR(kGrpA + s), 128);
-      mbar_init(BAR(kGrpB + s), 128);
-    }
+    mbar_init(BAR(kGrpB), kSoftmaxThreads);
     mbar_fence_init();
     fence_proxy_async_smem();
   }
@@ -227,9 +237,12 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
   const int seq_per_tile = p.packed ? (BLK / p.G) : BLK;  // sequence positions covered by one q tile
 
-  if (warp == kLoadWarp) {
-    // ======================================= TMA producer =======================================
+  if (warp == kLoadWarp || warp == kLoadWarp + 1) {
+    // ======================================= TMA producers ======================================
+    // One producer warp per stream: each fills only its own stream's ring, so a full ring of one stream
+    // never holds back the loads of the other.  Producer 0 also loads the Q tiles.
     setmaxnreg_dec<56>();
+    const int ls = warp - kLoadWarp;
     uint32_t ring_cnt[2] = {0, 0};  // tiles produced so far into each stream's ring
     uint32_t q_cnt = 0;
     bool ok = true;
@@ -241,22 +254,24 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const int n_it = t.it_end - t.it_begin;
       if (n_it <= 0) continue;
       PT_MARK(0)
-      // Q tile
-      ok = mbar_wait(BAR(kQEmpty), (q_cnt & 1) ^ 1, wctx, 100);
-      if (!ok) break;
-      PT_MARK(1)
-      if (lane == 0) {
-        // a 64-row query tile fills only the top half of each slab
-        mbar_arrive_expect_tx(BAR(kQFull), Cfg::kSlabs * BLK * 128);
+      if (ls == 0) {
+        // Q tile
+        ok = mbar_wait(BAR(kQEmpty), (q_cnt & 1) ^ 1, wctx, 100);
+        if (!ok) break;
+        PT_MARK(1)
+        if (lane == 0) {
+          // a 64-row query tile fills only the top half of each slab
+          mbar_arrive_expect_tx(BAR(kQFull), Cfg::kSlabs * BLK * 128);
 #pragma unroll
-        for (int sl = 0; sl < Cfg::kSlabs; ++sl) {
-          tma_load_5d(smem_u32(sQ + sl * Cfg::kSlabBytes), &tm_q, BAR(kQFull), sl * (128 / Cfg::kElt),
-                      t.g, t.m * seq_per_tile, t.hkv, t.b);
+          for (int sl = 0; sl < Cfg::kSlabs; ++sl) {
+            tma_load_5d(smem_u32(sQ + sl * Cfg::kSlabBytes), &tm_q, BAR(kQFull), sl * (128 / Cfg::kElt),
+                        t.g, t.m * seq_per_tile, t.hkv, t.b);
+          }
         }
+        ++q_cnt;
       }
-      ++q_cnt;
 
-      // K/V tiles in MMA consumption order: K0, K1, V0, K2, V1, ..., K(n-1), V(n-2), V(n-1)
+      // K/V tiles of this producer's stream in its consumption order: K(s), V(s), K(s+2), V(s+2), ...
       auto issue_tile = [&](const CUtensorMap* tm, int strm, int blk0, int blk1) -> bool {
         const uint32_t depth = strm ? (uint32_t)(NS - Cfg::kRing0) : (uint32_t)Cfg::kRing0;
         const uint32_t stage = (strm ? (uint32_t)Cfg::kRing0 : 0u) + ring_cnt[strm] % depth;
@@ -294,18 +309,11 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           j1 = (2 * it + 1 < t.count) ? t.row[2 * it + 1] : j0;
         }
       };
-      int j0, j1, pj0, pj1;
-      fetch(t.it_begin, pj0, pj1);
-      ok = issue_tile(&tm_k, 0, pj0, pj1);
-      for (int i = 0; i < n_it && ok; ++i) {
-        if (i + 1 < n_it) {
-          fetch(t.it_begin + i + 1, j0, j1);
-          ok = issue_tile(&tm_k, (i + 1) & 1, j0, j1);
-          if (!ok) break;
-        }
-        ok = issue_tile(&tm_v, i & 1, pj0, pj1);
-        pj0 = j0;
-        pj1 = j1;
+      for (int i = ls; i < n_it && ok; i += 2) {
+        int j0, j1;
+        fetch(t.it_begin + i, j0, j1);
+        ok = issue_tile(&tm_k, ls, j0, j1);
+        if (ok) ok = issue_tile(&tm_v, ls, j0, j1);
       }
     }
     PT_FLUSH(48)
@@ -315,6 +323,10 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     // so with a single issuer the tensor pipe idles during every barrier wait and commit; with two
     // issuers one stream's bookkeeping overlaps the other stream's MMAs.  Per stream the order
     // PV(i) -> QK(i+2) is program order of one thread, which is what the aliasing of P_s with S_s needs.
+    // The two issuers take turns: QK(0), QK(1), {PV(0),QK(2)}, {PV(1),QK(3)}, ... enter the tensor pipe
+    // as whole batches in iteration order.  Left to themselves the streams lock in phase (both in their
+    // softmax, then both in their MMAs, measured); batches handed over by a token keep them half a
+    // cycle apart, so one stream's softmax runs under the other stream's MMAs.
     setmaxnreg_dec<56>();
     const int s = warp - kMmaWarp;
     const uint32_t kFmt = (FP8 || p.f16) ? 0u : 1u;  // e4m3 (kind::f8f6f4) or f16 (kind::f16) = 0, bf16 = 1
@@ -324,11 +336,23 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint32_t ring_depth = s ? (uint32_t)(NS - Cfg::kRing0) : (uint32_t)Cfg::kRing0;
     const uint32_t ring_first = s ? (uint32_t)Cfg::kRing0 : 0u;
     bool ok = true;
+    uint32_t turn_cnt = 0;      // completed waits on this issuer's turn barrier
+    int prev_last_stream = -1;  // stream that issued the last batch of the previous non-empty tile
+    auto turn_wait = [&]() -> bool {
+      const bool r = mbar_wait(turn_base + 8u * s, turn_cnt & 1, wctx, 205);
+      ++turn_cnt;
+      return r;
+    };
+    auto turn_pass = [&]() {
+      if (lane == 0) mbar_arrive(turn_base + 8u * (s ^ 1));
+      __syncwarp();
+    };
     // descriptors are built once; a byte offset b inside a tile is an addition of b >> 4 to the low word
     const uint64_t q_desc = umma_desc_sw128(smem_u32(sQ), 0, 1024);
     const uint64_t k_desc0 = umma_desc_sw128(smem_u32(sKV), 0, 1024);                               // K-major view
     const uint64_t v_desc0 = umma_desc_sw128(smem_u32(sKV), FP8 ? 0u : (uint32_t)Cfg::kSlabBytes, 1024);  // MN-major
     PT_DECL
+    PT_TRACE_DECL
     for (int band = 0; band * (int)gridDim.x < p.num_work && ok; ++band) {
       const int w = snake_work(band);
       if (w >= p.num_work) continue;
@@ -341,12 +365,16 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       PT_MARK(1)
       ++q_cnt;
       // this stream's ring holds K(s), V(s), K(s+2), V(s+2), ... and is consumed in exactly that order
-      auto issue_qk = [&](int i) -> bool {
+      auto issue_qk = [&](int i, bool take_turn) -> bool {
         const uint32_t stage = ring_first + ring_pos % ring_depth;
         PT_MARK(0)
         if (!mbar_wait(BAR(kKvFull + stage), (ring_pos / ring_depth) & 1, wctx, 201)) return false;
         ++ring_pos;
         PT_MARK(2)
+        if (take_turn && !turn_wait()) return false;
+        PT_MARK(5)
+        PT_TRACE(4 + s, 0)
+        PT_MARK(0)
         if (lane == 0) {
           const uint64_t kd = k_desc0 + (uint64_t)stage * (Cfg::kTileBytes >> 4);
 #pragma unroll
@@ -357,13 +385,17 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if (FP8) umma_f8_ss(tS[s], q_desc + off, kd + off, idesc_qk, k > 0);
             else umma_f16_ss(tS[s], q_desc + off, kd + off, idesc_qk, k > 0);
           }
+          PT_TRACE(4 + s, 1)
           umma_commit(BAR(kSFull + s));
           umma_commit(BAR(kKvEmpty + stage));
         }
         __syncwarp();
+        PT_MARK(7)
+        PT_TRACE(4 + s, 2)
+        PT_TRACE_NEXT(4 + s)
         return true;
       };
-      auto issue_pv = [&](int i) -> bool {
+      auto issue_pv = [&](int i, bool take_turn) -> bool {
         const uint32_t stage = ring_first + ring_pos % ring_depth;
         PT_MARK(0)
         if (!mbar_wait(BAR(kKvFull + stage), (ring_pos / ring_depth) & 1, wctx, 202)) return false;
@@ -371,6 +403,9 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         PT_MARK(3)
         if (!mbar_wait(BAR(kPHalf + s), p_cnt & 1, wctx, 203)) return false;  // first half of P_s
         PT_MARK(4)
+        if (take_turn && !turn_wait()) return false;
+        PT_MARK(5)
+        PT_TRACE(2 + s, 0)
         tc_fence_after();
         const uint64_t vd = v_desc0 + (uint64_t)stage * (Cfg::kTileBytes >> 4);
         auto pv_steps = [&](int k0, int k1) {
@@ -382,34 +417,51 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             const uint32_t a_t = tS[s] + (uint32_t)k * Cfg::kPColsPerStep;
             if (FP8) umma_f8_ts(tO[s], a_t, db, idesc_pv, (i >= 2) || (k > 0));
             else umma_f16_ts(tO[s], a_t, db, idesc_pv, (i >= 2) || (k > 0));
+            if (k < 4) { PT_TRACE(6 + s, k & 3) }
           }
         };
+        PT_MARK(0)
         if (lane == 0) pv_steps(0, Cfg::kKSteps / 2);
         __syncwarp();
+        PT_MARK(6)
+        PT_TRACE(2 + s, 3)
+        PT_TRACE_NEXT(6 + s)
         PT_MARK(0)
         if (!mbar_wait(BAR(kPFull + s), p_cnt & 1, wctx, 204)) return false;  // second half
         PT_MARK(4)
         ++p_cnt;
         tc_fence_after();
+        PT_MARK(0)
         if (lane == 0) {
           pv_steps(Cfg::kKSteps / 2, Cfg::kKSteps);
           umma_commit(BAR(kKvEmpty + stage));
         }
         __syncwarp();
+        PT_MARK(6)
         return true;
       };
 
-      if (s < n_it) ok = issue_qk(s);
-      int last_qk = (s < n_it) ? s : -1;
+      // turns of this tile: QK(0) [stream 0], QK(1) [stream 1, if it has work], then batch i = {PV(i),
+      // QK(i+2)} by stream i & 1.  A turn waits for the token only if its predecessor belongs to the other
+      // issuer, and passes it only if its successor does (the successor of the last batch is QK(0) of the
+      // next tile with work, a turn of stream 0).
+      if (s == 0) {
+        ok = issue_qk(0, prev_last_stream == 1);
+        if (ok && n_it >= 2) turn_pass();
+      } else if (n_it >= 2) {
+        ok = issue_qk(1, true);
+        if (ok) turn_pass();
+      }
       for (int i = s; i < n_it && ok; i += 2) {
-        ok = issue_pv(i);
-        if (ok && i + 2 < n_it) {
-          ok = issue_qk(i + 2);
-          last_qk = i + 2;
-        }
+        ok = issue_pv(i, i >= 1 || n_it >= 2);
+        PT_TRACE(2 + s, 1)
+        if (ok && i + 2 < n_it) ok = issue_qk(i + 2, false);
+        if (ok && (i + 1 < n_it || s == 1)) turn_pass();
+        PT_TRACE(2 + s, 2)
+        PT_TRACE_NEXT(2 + s)
       }
       if (!ok) break;
-      (void)last_qk;
+      prev_last_stream = (n_it - 1) & 1;
       // Q is free once the QK MMAs of BOTH streams have completed: each issuer signals for its own MMAs
       // (a stream without work arrives directly; it cannot arrive twice in one phase because the next Q
       // tile, which it waits for first, is only loaded after this phase has completed).  O_s is final
@@ -433,12 +485,13 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const int row = threadIdx.x & 127;         // query row inside the tile = tensor-memory lane
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     const bool row_active = (BLK == 128) || (row < 64);  // warp-uniform
-    uint32_t s_cnt = 0, of_cnt[2] = {0, 0}, epi_a = 0, epi_b = 0, grp_a = 0, grp_b = 0;
+    uint32_t s_cnt = 0, of_cnt[2] = {0, 0}, epi_a = 0, grp_b = 0;
     bool ok = true;
     const bool need_mask_meta = (p.block_sizes != nullptr) || (p.Sk % BLK != 0);
     constexpr float kRescaleThreshold = FP8 ? 1.8073549f /* log2(448/128) */ : 8.0f;
     constexpr float kPBias = FP8 ? 7.0f : 0.0f;
     PT_DECL
+    PT_TRACE_DECL
 
     for (int band = 0; band * (int)gridDim.x < p.num_work && ok; ++band) {
       const int w = snake_work(band);
@@ -501,6 +554,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         ok = mbar_wait(BAR(kSFull + grp), s_cnt & 1, wctx, 300 + grp);
         if (!ok) break;
         PT_MARK(1)
+        if ((warp & 3) == 0) { PT_TRACE(grp, 0) }
         ++s_cnt;
         tc_fence_after();
         if (!row_active) {
@@ -633,6 +687,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const float m_used = (m_cur == -INFINITY) ? 0.f : m_cur;
         const float neg_m = kPBias - m_used;
         PT_MARK(3)
+        if ((warp & 3) == 0) { PT_TRACE(grp, 1) }
         // ---- exponentials, row sum, P to tensor memory
         float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
         if (FP8) {
@@ -723,15 +778,32 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         l_sum += (a0 + a1) + (a2 + a3);
         PT_MARK(4)
+        if ((warp & 3) == 0) { PT_TRACE(grp, 2) }
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(BAR(kPFull + grp));
         PT_MARK(5)
+        if ((warp & 3) == 0) { PT_TRACE(grp, 3) PT_TRACE_NEXT(grp) }
       }
       if (!ok) break;
 
       // ------------------------------------ tile epilogue ------------------------------------
       PT_MARK(0)
+      // The (max, sum) pairs of the two streams are exchanged while the last PV MMAs are still running.
+      // The same rendezvous orders this tile's staging writes after the previous tile's output store.
+      s_stats[grp][row] = make_float2(m_cur, l_sum);
+      if (!SPLIT && (threadIdx.x & 127) == 0) tma_store_wait_read<0>();
+      ok = mbar_rendezvous_poll(BAR(kEpiA), epi_a, wctx, 320);
+      if (!ok) break;
+      const float2 st0 = s_stats[0][row];
+      const float2 st1 = s_stats[1][row];
+      const float m_all = fmaxf(st0.x, st1.x);
+      const float w0 = (st0.x == -INFINITY) ? 0.f : ex2_approx(st0.x - m_all);
+      const float w1 = (st1.x == -INFINITY) ? 0.f : ex2_approx(st1.x - m_all);
+      const float denom = st0.y * w0 + st1.y * w1;
+      const float inv = (denom > 0.f) ? (1.f / denom) : 0.f;
+      const float f0 = w0 * inv, f1 = w1 * inv;
+      const bool has0 = n_it > 0, has1 = n_it > 1;
       if (n_it > 0) {
         ok = mbar_wait(BAR(kOFinal), of_cnt[0] & 1, wctx, 310 + grp);
         if (!ok) break;
@@ -744,18 +816,6 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         tc_fence_after();
       }
       PT_MARK(6)
-      s_stats[grp][row] = make_float2(m_cur, l_sum);
-      ok = mbar_rendezvous(BAR(kEpiA), epi_a, wctx, 320);
-      if (!ok) break;
-      const float2 st0 = s_stats[0][row];
-      const float2 st1 = s_stats[1][row];
-      const float m_all = fmaxf(st0.x, st1.x);
-      const float w0 = (st0.x == -INFINITY) ? 0.f : ex2_approx(st0.x - m_all);
-      const float w1 = (st1.x == -INFINITY) ? 0.f : ex2_approx(st1.x - m_all);
-      const float denom = st0.y * w0 + st1.y * w1;
-      const float inv = (denom > 0.f) ? (1.f / denom) : 0.f;
-      const float f0 = w0 * inv, f1 = w1 * inv;
-      const bool has0 = n_it > 0, has1 = n_it > 1;
 
       // this group finalises output columns [64*grp, 64*grp+64)
       float acc[64];
@@ -780,9 +840,6 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
       }
       tc_fence_before();
-      // all reads of O0/O1 and of the stats are done: the next tile may overwrite them
-      ok = mbar_rendezvous(BAR(kEpiB), epi_b, wctx, 321);
-      if (!ok) break;
 
       if (FP8) {
         const float* vs = p.v_scale + (long long)hq * 128 + grp * 64;
@@ -800,12 +857,12 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             dst[e] = make_float4(acc[4 * e], acc[4 * e + 1], acc[4 * e + 2], acc[4 * e + 3]);
           if (grp == 0) p.partial_lse[prow] = lse_log2 * kLn2;
         }
+        // every thread has read its share of O0 / O1: the next tile may overwrite them
+        ok = mbar_rendezvous_poll(BAR(kGrpB), grp_b, wctx, 323);
+        if (!ok) break;
       } else {
         // stage bf16 in shared memory in the 128-byte-swizzled layout the output tensor map expects
         const bool issuer = (threadIdx.x & 127) == 0;
-        if (issuer) tma_store_wait_read<0>();
-        ok = mbar_rendezvous(BAR(kGrpA + grp), grp_a, wctx, 322);
-        if (!ok) break;
         if (row_active) {
           uint8_t* slab = sO + grp * (128 * 128);
 #pragma unroll
@@ -826,7 +883,9 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
         }
         fence_proxy_async_smem();
-        ok = mbar_rendezvous(BAR(kGrpB + grp), grp_b, wctx, 323);
+        // both groups: the staging tile is complete, and every thread has read its share of O0 / O1, so the
+        // next tile may overwrite them
+        ok = mbar_rendezvous_poll(BAR(kGrpB), grp_b, wctx, 323);
         if (!ok) break;
         if (issuer) {
           const int cs = t.m * seq_per_tile;
