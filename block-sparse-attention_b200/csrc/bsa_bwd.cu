@@ -138,6 +138,24 @@ __device__ __forceinline__ void store_row_half(__nv_bfloat16* dst, const uint32_
   }
 }
 
+// Of every four column pairs of a probability row, this many take the polynomial exp2 on the FMA pipe
+// instead of the special-function unit.  Both compute groups of a kernel recompute their 64 columns at the
+// same time on the same four schedulers, so the phase is bound by the special-function unit (16 results
+// per clock per SM) unless a share of it moves to the FMA pipe.
+#ifndef BSA_BWD_EX2_EMU4
+#define BSA_BWD_EX2_EMU4 0
+#endif
+
+// exp2 of two scaled-and-shifted scores (pair index `pair` selects the unit that computes them)
+__device__ __forceinline__ void exp2_pair(int pair, float x0, float x1, float& y0, float& y1) {
+  if ((pair & 3) < BSA_BWD_EX2_EMU4) {
+    unpack2(ex2_emu2(x0, x1), y0, y1);
+  } else {
+    y0 = ex2_approx(x0);
+    y1 = ex2_approx(x1);
+  }
+}
+
 constexpr uint32_t kIdescKK = umma_idesc(1, 1, 0, 0, 128, 128);   // A K-major, B K-major
 constexpr uint32_t kIdescKMN = umma_idesc(1, 1, 0, 1, 128, 128);  // A K-major (smem or tmem), B MN-major
 
@@ -175,7 +193,7 @@ __device__ __forceinline__ void mma_ts_kmn(uint32_t d, uint32_t a_lo, uint32_t a
 // ------------------------------------------------------------------------------------------------
 // 2. dQ kernel
 // ------------------------------------------------------------------------------------------------
-// smem: Q | dO | ring of 5 tiles (K_j, V_j alternating; the V_j slot is reused for dS_j) | barriers | misc
+// smem: Q | dO | ring of 5 tiles (K_j, V_j alternating) | barriers | misc
 constexpr int kDqStages = 5;
 constexpr int kDqSmem = 2 * kTile + kDqStages * kTile + BwdSmem::kBarBytes + BwdSmem::kMisc;
 
@@ -324,6 +342,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (lane == 0) {
           mma_ss_kk(tdP, ddo_desc, ring_k + stage_of(base + 2 * j + 1) * kTileDescStep, false);
           umma_commit(BAR(kDpFull));
+          umma_commit(BAR(kREmpty + stage_of(base + 2 * j + 1)));  // V_j is only read by this MMA
         }
         __syncwarp();
         return true;
@@ -337,10 +356,6 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (!ok) break;
         PT_MARK(3)
         ++ds_cnt;
-        if (j + 1 < n) {
-          ok = issue_dp(j + 1);
-          if (!ok) break;
-        }
         if (j == 0 && !first_tile) {  // the previous tile's epilogue has drained dQ
           PT_MARK(0)
           ok = mbar_wait(BAR(kDqFree), free_cnt & 1, wctx, 413);
@@ -350,13 +365,17 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
         tc_fence_after();
         if (lane == 0) {
-          const uint32_t sk = stage_of(base + 2 * j), sv = stage_of(base + 2 * j + 1);
-          // dQ += dS_j (staged in the V_j slot, K-major) * K_j (MN-major view of the K tile)
-          mma_ss_kmn(tdQ, ring_k + sv * kTileDescStep, ring_mn + sk * kTileDescStep, j > 0);
+          const uint32_t sk = stage_of(base + 2 * j);
+          // dQ += dS_j (bf16 in tensor memory, at the head of each group's half of the dP columns) * K_j
+          // (MN-major view of the K tile)
+          mma_ts_kmn(tdQ, tdP, tdP + 64u, ring_mn + sk * kTileDescStep, j > 0);
           umma_commit(BAR(kREmpty + sk));
-          umma_commit(BAR(kREmpty + sv));
         }
         __syncwarp();
+        if (j + 1 < n) {
+          ok = issue_dp(j + 1);  // overwrites dS_j: in program order after the dQ MMAs that read it
+          if (!ok) break;
+        }
         if (j + 2 < n) ok = issue_s(j + 2);
       }
       if (!ok) break;
@@ -430,12 +449,13 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
         const float neg_l = -lse2;
 #pragma unroll
-        for (int c = 0; c < 64; ++c) pr[c] = ex2_approx(fmaf(pr[c], p.scale_log2, neg_l));
+        for (int c = 0; c < 64; c += 2)
+          exp2_pair(c >> 1, fmaf(pr[c], p.scale_log2, neg_l), fmaf(pr[c + 1], p.scale_log2, neg_l), pr[c], pr[c + 1]);
         if (len < 64) {
 #pragma unroll
           for (int c = 0; c < 64; ++c) pr[c] = (c < len) ? pr[c] : 0.f;
         }
-        // ---- phase 2: dS = P o (dP - delta) -> bf16 -> shared memory (the V_j slot, K-major, swizzled)
+        // ---- phase 2: dS = P o (dP - delta) -> bf16 -> tensor memory (head of this group's half of dP)
         PT_MARK(2)
         ok = mbar_wait(BAR(kDpFull), dp_cnt & 1, wctx, 421);
         if (!ok) break;
@@ -446,20 +466,17 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tmem_ld32(tdP + lane_base + grp * 64, dp);
         tmem_ld32(tdP + lane_base + grp * 64 + 32, dp + 32);
         tmem_wait_ld();
-        uint8_t* slab = sRing + ((base + 2 * j + 1) % NS) * kTile + grp * kSlab;
+        {
+          uint32_t pk[32];
 #pragma unroll
-        for (int ch = 0; ch < 8; ++ch) {
-          float d[8];
-#pragma unroll
-          for (int e = 0; e < 8; ++e) d[e] = pr[ch * 8 + e] * (__uint_as_float(dp[ch * 8 + e]) - dlt);
-          uint4 v;
-          v.x = pack_bf16x2(d[0], d[1]);
-          v.y = pack_bf16x2(d[2], d[3]);
-          v.z = pack_bf16x2(d[4], d[5]);
-          v.w = pack_bf16x2(d[6], d[7]);
-          *reinterpret_cast<uint4*>(slab + row * 128 + ((ch ^ (row & 7)) << 4)) = v;
+          for (int e = 0; e < 32; ++e) {
+            const float d0 = pr[2 * e] * (__uint_as_float(dp[2 * e]) - dlt);
+            const float d1 = pr[2 * e + 1] * (__uint_as_float(dp[2 * e + 1]) - dlt);
+            pk[e] = pack_bf16x2(d0, d1);
+          }
+          tmem_st32(tdP + lane_base + grp * 64, pk);
+          tmem_wait_st();
         }
-        fence_proxy_async_smem();
         tc_fence_before();
         mbar_arrive(BAR(kDsFull));
         PT_MARK(4)
@@ -820,10 +837,10 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
         for (int c4 = 0; c4 < 16; ++c4) {
           const float4 l = st_l[c4];
-          pr[c4 * 4 + 0] = ex2_approx(fmaf(pr[c4 * 4 + 0], p.scale_log2, -l.x));
-          pr[c4 * 4 + 1] = ex2_approx(fmaf(pr[c4 * 4 + 1], p.scale_log2, -l.y));
-          pr[c4 * 4 + 2] = ex2_approx(fmaf(pr[c4 * 4 + 2], p.scale_log2, -l.z));
-          pr[c4 * 4 + 3] = ex2_approx(fmaf(pr[c4 * 4 + 3], p.scale_log2, -l.w));
+          exp2_pair(2 * c4, fmaf(pr[c4 * 4 + 0], p.scale_log2, -l.x), fmaf(pr[c4 * 4 + 1], p.scale_log2, -l.y),
+                    pr[c4 * 4 + 0], pr[c4 * 4 + 1]);
+          exp2_pair(2 * c4 + 1, fmaf(pr[c4 * 4 + 2], p.scale_log2, -l.z), fmaf(pr[c4 * 4 + 3], p.scale_log2, -l.w),
+                    pr[c4 * 4 + 2], pr[c4 * 4 + 3]);
         }
         // masked KV token, or the phantom second half of an odd pair
         if (!kv_live || (BLK == 64 && grp == 1 && 2 * i + 1 >= entries)) {
