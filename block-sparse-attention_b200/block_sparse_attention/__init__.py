@@ -17,6 +17,10 @@ _EXPORTS = {
     "block_sparse_attention": ".autograd",
     "HostPipeline": ".host_pipeline",
     "BlockSparseAttentionFunction": ".autograd",
+    "block_mean": ".topk_index",
+    "pooled_scores": ".topk_index",
+    "topk_q2k": ".topk_index",
+    "pooled_topk_q2k": ".topk_index",
 }
 
 __all__ = sorted(_EXPORTS)

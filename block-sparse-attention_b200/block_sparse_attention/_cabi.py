@@ -129,6 +129,9 @@ SIGNATURES = {
     "bsa_lpt_order": (ctypes.c_int, [_vp, _i32, _i32, _vp, _vp, _vp]),
     "bsa_lpt_order_scratch_ints": (ctypes.c_int64, [_i32, _i32]),
     "bsa_build_k2q_csr": (ctypes.c_int, [_vp, _vp, _i32, _i32, _i32, _i32, _i32, _i32, _i32, _vp, _vp, _vp]),
+    "bsa_block_mean": (ctypes.c_int, [_vp, ctypes.POINTER(ctypes.c_int64), _i32, _i32, _i32, _i32, _i32, _vp, _vp]),
+    "bsa_pooled_scores": (ctypes.c_int, [_vp, _vp, _i32, _i32, _i32, _i32, ctypes.c_float, _vp, _vp]),
+    "bsa_topk_q2k": (ctypes.c_int, [_vp, ctypes.c_int64, _i32, _i32, _i32, _vp, _vp]),
     "bsa_bwd": (ctypes.c_int, [ctypes.POINTER(BwdArgs), _vp]),
     "bsa_bwd_workspace_bytes": (ctypes.c_int64, [_i32, _i32, _i32, _i32, _i32]),
 }

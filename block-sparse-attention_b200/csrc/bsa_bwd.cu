@@ -63,41 +63,60 @@ struct BwdParams {
 // ------------------------------------------------------------------------------------------------
 // 1. preprocess
 // ------------------------------------------------------------------------------------------------
-// one warp per padded row; lane l holds 4 channels
+// HBM-bound: reads O and dO once.  A warp handles eight consecutive padded rows: sixteen lanes per row with
+// 16 bytes each, all eight loads of a thread in flight before the first use.
+constexpr int kPreRowsPerWarp = 8;
 __global__ void __launch_bounds__(256)
 bwd_preprocess_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                       const float* __restrict__ lse, float* __restrict__ lse_log2, float* __restrict__ delta,
                       long long os_b, long long os_h, long long os_s, long long ds_b, long long ds_h, long long ds_s,
                       int H, int Sq, int SqPad, long long rows_pad) {
-  const long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
-  if (row >= rows_pad) return;
+  const long long row0 = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * kPreRowsPerWarp;
+  if (row0 >= rows_pad) return;
   const int lane = threadIdx.x & 31;
-  const int s = (int)(row % SqPad);
-  const long long bh = row / SqPad;
-  const int h = (int)(bh % H);
-  const long long b = bh / H;
-  float acc = 0.f;
-  float l = INFINITY;
-  if (s < Sq) {
-    const uint2 ov = *reinterpret_cast<const uint2*>(o + b * os_b + h * os_h + (long long)s * os_s + lane * 4);
-    const uint2 dv = *reinterpret_cast<const uint2*>(d_o + b * ds_b + h * ds_h + (long long)s * ds_s + lane * 4);
-    const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov);
-    const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&dv);
+  const int sub = lane >> 4, chunk = lane & 15;  // two rows per pass, sixteen 16-byte chunks per row
+  uint4 ov[4], dv[4];
+  bool live[4];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      const float2 a = __bfloat1622float2(o2[i]);
-      const float2 c = __bfloat1622float2(d2[i]);
+  for (int i = 0; i < 4; ++i) {
+    const long long row = row0 + 2 * i + sub;
+    const int s = (int)(row % SqPad);
+    const long long bh = row / SqPad;
+    const int h = (int)(bh % H);
+    const long long b = bh / H;
+    live[i] = row < rows_pad && s < Sq;
+    ov[i] = make_uint4(0, 0, 0, 0);
+    dv[i] = make_uint4(0, 0, 0, 0);
+    if (live[i]) {
+      ov[i] = *reinterpret_cast<const uint4*>(o + b * os_b + h * os_h + (long long)s * os_s + chunk * 8);
+      dv[i] = *reinterpret_cast<const uint4*>(d_o + b * ds_b + h * ds_h + (long long)s * ds_s + chunk * 8);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const long long row = row0 + 2 * i + sub;
+    const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov[i]);
+    const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&dv[i]);
+    float acc = 0.f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 a = __bfloat1622float2(o2[e]);
+      const float2 c = __bfloat1622float2(d2[e]);
       acc = fmaf(a.x, c.x, acc);
       acc = fmaf(a.y, c.y, acc);
     }
-    const float lv = lse[bh * Sq + s];
-    l = (lv == -INFINITY) ? INFINITY : lv * kLog2e;
-  }
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (lane == 0) {
-    delta[row] = acc;
-    lse_log2[row] = l;
+    for (int off = 8; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);  // within the half warp
+    if (chunk == 0 && row < rows_pad) {
+      float l = INFINITY;
+      if (live[i]) {
+        const int s = (int)(row % SqPad);
+        const float lv = lse[(row / SqPad) * Sq + s];
+        l = (lv == -INFINITY) ? INFINITY : lv * kLog2e;
+      }
+      delta[row] = acc;
+      lse_log2[row] = l;
+    }
   }
 }
 
@@ -966,7 +985,7 @@ extern "C" int bsa_bwd(const bsa_bwd_args* a, void* cuda_stream) {
   const long long rows_pad = (long long)a->B * a->H * Nq * blk;
   float* lse_log2 = reinterpret_cast<float*>(a->workspace);
   float* delta = lse_log2 + rows_pad;
-  bwd_preprocess_kernel<<<(unsigned)((rows_pad + 7) / 8), 256, 0, st>>>(
+  bwd_preprocess_kernel<<<(unsigned)((rows_pad + 8 * kPreRowsPerWarp - 1) / (8 * kPreRowsPerWarp)), 256, 0, st>>>(
       reinterpret_cast<const __nv_bfloat16*>(a->out), reinterpret_cast<const __nv_bfloat16*>(a->dout), a->lse, lse_log2,
       delta, a->o_stride[0], a->o_stride[1], a->o_stride[2], a->do_stride[0], a->do_stride[1], a->do_stride[2], a->H,
       a->Sq, Nq * blk, rows_pad);

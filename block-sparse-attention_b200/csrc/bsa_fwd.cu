@@ -329,6 +329,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     // cycle apart, so one stream's softmax runs under the other stream's MMAs.
     setmaxnreg_dec<56>();
     const int s = warp - kMmaWarp;
+    const uint32_t tS_s = tmem + 128u * (uint32_t)s, tO_s = tmem + 256u + 128u * (uint32_t)s;
     const uint32_t kFmt = (FP8 || p.f16) ? 0u : 1u;  // e4m3 (kind::f8f6f4) or f16 (kind::f16) = 0, bf16 = 1
     const uint32_t idesc_qk = umma_idesc(kFmt, kFmt, 0, 0, 128, 128);
     const uint32_t idesc_pv = umma_idesc(kFmt, kFmt, 0, 1, 128, 128);
@@ -375,21 +376,18 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         PT_MARK(5)
         PT_TRACE(4 + s, 0)
         PT_MARK(0)
-        if (lane == 0) {
+        {
+          const uint32_t led = lane == 0;
           const uint64_t kd = k_desc0 + (uint64_t)stage * (Cfg::kTileBytes >> 4);
 #pragma unroll
           for (int k = 0; k < Cfg::kKSteps; ++k) {
-            // 32 bytes of K extent per step inside a 128-byte swizzled row; bf16 tiles continue in
-            // the second slab after four steps.
             const uint64_t off = FP8 ? (uint64_t)(k * 2) : (uint64_t)((k >> 2) * (Cfg::kSlabBytes >> 4) + (k & 3) * 2);
-            if (FP8) umma_f8_ss(tS[s], q_desc + off, kd + off, idesc_qk, k > 0);
-            else umma_f16_ss(tS[s], q_desc + off, kd + off, idesc_qk, k > 0);
+            if (FP8) umma_f8_ss_led(tS_s, q_desc + off, kd + off, idesc_qk, k > 0, led);
+            else umma_f16_ss_led(tS_s, q_desc + off, kd + off, idesc_qk, k > 0, led);
           }
-          PT_TRACE(4 + s, 1)
-          umma_commit(BAR(kSFull + s));
-          umma_commit(BAR(kKvEmpty + stage));
+          umma_commit_led(BAR(kSFull + s), led);
+          umma_commit_led(BAR(kKvEmpty + stage), led);
         }
-        __syncwarp();
         PT_MARK(7)
         PT_TRACE(4 + s, 2)
         PT_TRACE_NEXT(4 + s)
@@ -414,15 +412,14 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             // V is MN-major: one k step = kMmaK token rows of 128 B; the second 64-channel slab of a
             // bf16 tile is reached through the leading byte offset.
             const uint64_t db = vd + (uint64_t)(k * ((Cfg::kMmaK * 128) >> 4));
-            const uint32_t a_t = tS[s] + (uint32_t)k * Cfg::kPColsPerStep;
-            if (FP8) umma_f8_ts(tO[s], a_t, db, idesc_pv, (i >= 2) || (k > 0));
-            else umma_f16_ts(tO[s], a_t, db, idesc_pv, (i >= 2) || (k > 0));
+            const uint32_t a_t = tS_s + (uint32_t)k * Cfg::kPColsPerStep;
+            if (FP8) umma_f8_ts_led(tO_s, a_t, db, idesc_pv, (i >= 2) || (k > 0), lane == 0);
+            else umma_f16_ts_led(tO_s, a_t, db, idesc_pv, (i >= 2) || (k > 0), lane == 0);
             if (k < 4) { PT_TRACE(6 + s, k & 3) }
           }
         };
         PT_MARK(0)
-        if (lane == 0) pv_steps(0, Cfg::kKSteps / 2);
-        __syncwarp();
+        pv_steps(0, Cfg::kKSteps / 2);
         PT_MARK(6)
         PT_TRACE(2 + s, 3)
         PT_TRACE_NEXT(6 + s)
@@ -432,11 +429,8 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         ++p_cnt;
         tc_fence_after();
         PT_MARK(0)
-        if (lane == 0) {
-          pv_steps(Cfg::kKSteps / 2, Cfg::kKSteps);
-          umma_commit(BAR(kKvEmpty + stage));
-        }
-        __syncwarp();
+        pv_steps(Cfg::kKSteps / 2, Cfg::kKSteps);
+        umma_commit_led(BAR(kKvEmpty + stage), lane == 0);
         PT_MARK(6)
         return true;
       };

@@ -180,6 +180,27 @@ int bsa_lpt_order(const int32_t* q2k_nums, int32_t rows, int32_t cap, int32_t* o
 int64_t bsa_lpt_order_scratch_ints(int32_t rows, int32_t cap);
 
 /*
+ * Top-k block selection, the step that produces the q2k index.  The reference has no kernel for it: its
+ * benchmark builds the index with torch (tests/bench_cutedsl_performance.py:131-167: pooled scores ->
+ * torch.topk(sorted=False) -> ascending sort -> int32) and its notes name the recipe (design/fp8/results.md:
+ * 635-636: mean-pool, top-k, complete K-block index layout).
+ *   bsa_block_mean:    x [B,H,S,D] bf16 with element strides (b,h,s; last stride 1) -> out [B,H,ceil(S/blk),D]
+ *                      fp32, the mean of every blk consecutive tokens (a short tail averages what exists).
+ *   bsa_pooled_scores: scores[bh,m,j] = scale * sum_d qm[bh,m,d] * km[bh,j,d], fp32, summed in ascending d.
+ *   bsa_topk_q2k:      index[row, 0..k) = ids of the k largest scores of the row in ascending id order; among
+ *                      equal scores the lower id wins, NaN ranks above +inf (torch.topk's convention);
+ *                      index has row stride cap >= k, entries [k, cap) are left untouched.
+ *                      Limits: Nkv <= BSA_TOPK_MAX_BLOCKS, k <= 4096.
+ */
+#define BSA_TOPK_MAX_BLOCKS 8192
+int bsa_block_mean(const void* x, const int64_t* stride, int32_t B, int32_t H, int32_t S, int32_t D,
+                   int32_t blk, float* out, void* cuda_stream);
+int bsa_pooled_scores(const float* qm, const float* km, int32_t BH, int32_t Nq, int32_t Nkv, int32_t D,
+                      float scale, float* scores, void* cuda_stream);
+int bsa_topk_q2k(const float* scores, int64_t rows, int32_t Nkv, int32_t k, int32_t cap, int32_t* index,
+                 void* cuda_stream);
+
+/*
  * Bucketed k2q CSR for the backward pass.  offsets [B,H,G,Nkv+1] (running per (b,h) across the G
  * query groups of bucket_size_blocks q-blocks), indices [B,H,max(1,Nq*cap)] global q-block ids, every
  * CSR row in ascending q order (deterministic).  One edge per occurrence (q, position < count) whose id is

@@ -200,6 +200,28 @@ def attention_gathered_packed(q, k, v, index, count, nums=None, sizes=None, scal
 
 
 # --------------------------------------------------------------------------------------------------
+# top-k index producer
+# --------------------------------------------------------------------------------------------------
+def block_mean(x, blk):
+    """fp32 mean of every ``blk`` consecutive tokens of a BHSD tensor (a short tail averages what exists)."""
+    B, H, S, D = x.shape
+    N = ceil_div(S, blk)
+    xf = x.float()
+    out = torch.empty((B, H, N, D), dtype=torch.float32)
+    for n in range(N):
+        out[:, :, n] = xf[:, :, n * blk:(n + 1) * blk].mean(dim=2)
+    return out
+
+
+def topk_q2k(scores, topk):
+    """ids of the ``topk`` largest scores per row, ascending; ties go to the lower id.  Restates the recipe of
+    tests/bench_cutedsl_performance.py:150-167 (``torch.topk(sorted=False)`` then ``sort``) with a defined
+    tie rule: a stable descending sort keeps equal scores in id order."""
+    order = torch.sort(scores, dim=-1, descending=True, stable=True).indices[..., :topk]
+    return order.sort(dim=-1).values.to(torch.int32)
+
+
+# --------------------------------------------------------------------------------------------------
 # backward reference
 # --------------------------------------------------------------------------------------------------
 def backward_dense(q, k, v, dout, attn_bias, softmax_scale, upcast=True):

@@ -206,6 +206,15 @@ def main():
                         dout=bf16_bits(do), index=index.numpy(), nums=nums.numpy(), sizes=sizes.numpy(),
                         out=o.float().numpy(), lse=lse.numpy(), dq=dq.numpy(), dk=dk.numpy(), dv=dv.numpy())
 
+    # ---------------------------------------------------------------- I. top-k index recipe of the reference's benchmark
+    # tests/bench_cutedsl_performance.py:150-167 restated with a CPU generator (the file itself draws on CUDA):
+    # pooled scores ~ N(0,1) -> torch.topk(sorted=False) -> ascending sort -> int32
+    g = torch.Generator().manual_seed(31)
+    pooled = torch.randn(2, 3, 40, 300, generator=g)
+    selected = torch.topk(pooled, 37, dim=-1, sorted=False).indices
+    np.savez_compressed(os.path.join(HERE, "topk_q2k.npz"), scores=pooled.numpy(),
+                        index=selected.sort(dim=-1).values.to(torch.int32).numpy())
+
     # ---------------------------------------------------------------- H. split policy table
     counts = [1, 2, 31, 255, 256, 449, 450, 899, 900, 2048]
     table = [ref_iface._sm100_blk64_kv_splits_from_count(c) for c in counts]

@@ -155,6 +155,17 @@ def test_backward_64_token_blocks_with_block_sizes_matches_reference():
         assert torch.allclose(got, torch.from_numpy(g[name]), atol=2e-4, rtol=1e-4), name
 
 
+def test_topk_index_recipe_matches_torch_topk():
+    g = load_golden("topk_q2k.npz")
+    scores, ref = torch.from_numpy(g["scores"]), torch.from_numpy(g["index"])
+    assert torch.equal(orc.topk_q2k(scores, ref.shape[-1]), ref)
+    tied = torch.tensor([[1.0, 3.0, 3.0, 3.0, 0.0, 3.0]])
+    assert orc.topk_q2k(tied, 3).tolist() == [[1, 2, 3]]
+    x = torch.arange(2 * 1 * 5 * 4, dtype=torch.float32).reshape(2, 1, 5, 4).bfloat16()
+    m = orc.block_mean(x, 2)
+    assert m.shape == (2, 1, 3, 4) and torch.equal(m[0, 0, 2], x[0, 0, 4].float())
+
+
 def test_split_policy_matches_reference():
     g = load_golden("policy_blk64_splits.npz")
     for c, s in zip(g["counts"].tolist(), g["splits"].tolist()):
