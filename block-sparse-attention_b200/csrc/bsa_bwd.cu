@@ -75,26 +75,27 @@ bwd_preprocess_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* 
   if (row0 >= rows_pad) return;
   const int lane = threadIdx.x & 31;
   const int sub = lane >> 4, chunk = lane & 15;  // two rows per pass, sixteen 16-byte chunks per row
+  // the eight rows of a warp lie in one (batch, head) plane: the padded length is a multiple of 64
+  const long long bh = row0 / SqPad;
+  const int s0 = (int)(row0 - bh * SqPad);
+  const int h = (int)(bh % H);
+  const long long b = bh / H;
+  const __nv_bfloat16* o_base = o + b * os_b + h * os_h + chunk * 8;
+  const __nv_bfloat16* d_base = d_o + b * ds_b + h * ds_h + chunk * 8;
   uint4 ov[4], dv[4];
-  bool live[4];
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const long long row = row0 + 2 * i + sub;
-    const int s = (int)(row % SqPad);
-    const long long bh = row / SqPad;
-    const int h = (int)(bh % H);
-    const long long b = bh / H;
-    live[i] = row < rows_pad && s < Sq;
+    const int s = s0 + 2 * i + sub;
     ov[i] = make_uint4(0, 0, 0, 0);
     dv[i] = make_uint4(0, 0, 0, 0);
-    if (live[i]) {
-      ov[i] = *reinterpret_cast<const uint4*>(o + b * os_b + h * os_h + (long long)s * os_s + chunk * 8);
-      dv[i] = *reinterpret_cast<const uint4*>(d_o + b * ds_b + h * ds_h + (long long)s * ds_s + chunk * 8);
+    if (s < Sq) {
+      ov[i] = *reinterpret_cast<const uint4*>(o_base + (long long)s * os_s);
+      dv[i] = *reinterpret_cast<const uint4*>(d_base + (long long)s * ds_s);
     }
   }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const long long row = row0 + 2 * i + sub;
+    const int s = s0 + 2 * i + sub;
     const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&ov[i]);
     const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&dv[i]);
     float acc = 0.f;
@@ -107,15 +108,14 @@ bwd_preprocess_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* 
     }
 #pragma unroll
     for (int off = 8; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);  // within the half warp
-    if (chunk == 0 && row < rows_pad) {
+    if (chunk == 0) {
       float l = INFINITY;
-      if (live[i]) {
-        const int s = (int)(row % SqPad);
-        const float lv = lse[(row / SqPad) * Sq + s];
+      if (s < Sq) {
+        const float lv = lse[bh * Sq + s];
         l = (lv == -INFINITY) ? INFINITY : lv * kLog2e;
       }
-      delta[row] = acc;
-      lse_log2[row] = l;
+      delta[bh * SqPad + s] = acc;
+      lse_log2[bh * SqPad + s] = l;
     }
   }
 }
