@@ -17,6 +17,7 @@ _EXPORTS = {
     "block_sparse_attention": ".autograd",
     "HostPipeline": ".host_pipeline",
     "BlockSparseAttentionFunction": ".autograd",
+    "block_sparse_attention_op": ".torch_ops",
     "block_mean": ".topk_index",
     "pooled_scores": ".topk_index",
     "topk_q2k": ".topk_index",

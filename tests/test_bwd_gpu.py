@@ -238,6 +238,33 @@ def test_autograd_function_64_token_blocks():
     _check(tuple(t.grad.float().cpu() for t in (qc, kc, vc)), q, k, v, do, bias, 1 / math.sqrt(128))
 
 
+def test_custom_op_matches_functional_calls_and_compiles():
+    from block_sparse_attention import block_sparse_attention_op, bsa_attn_bwd, bsa_attn_fwd
+    q, k, v, do, index, nums = _case(13, 1, 2, 384, 512, [3, 1, 4], poison=False)
+    ic, nc, doc = index.cuda(), nums.cuda(), do.cuda()
+    qc, kc, vc = (t.cuda().requires_grad_() for t in (q, k, v))
+    out = block_sparse_attention_op(qc, kc, vc, ic, 0, q2k_block_nums=nc)
+    out.backward(doc)
+    ref_out, lse = bsa_attn_fwd(qc.detach(), kc.detach(), vc.detach(), ic, 0, q2k_block_nums=nc, return_lse=True,
+                                sparse_block_size=128)
+    ref = bsa_attn_bwd(doc, qc.detach(), kc.detach(), vc.detach(), ref_out, lse, ic, 0, q2k_block_nums=nc,
+                       sparse_block_size=128)
+    assert torch.equal(out, ref_out)
+    for t, r in zip((qc, kc, vc), ref):
+        assert torch.equal(t.grad, r)
+    # traced as one opaque node: the graph backend only has to carry the call (no code generation involved)
+    fn = torch.compile(lambda a, b, c: block_sparse_attention_op(a, b, c, ic, 0, q2k_block_nums=nc) * 2.0,
+                       backend="aot_eager", fullgraph=True)
+    q2, k2, v2 = (t.detach().clone().requires_grad_() for t in (qc, kc, vc))
+    out2 = fn(q2, k2, v2)
+    out2.backward(doc)
+    assert torch.equal(out2, ref_out * 2.0)
+    assert torch.allclose(q2.grad.float(), 2 * ref[0].float(), rtol=1e-2, atol=1e-3)
+    torch.library.opcheck(torch.ops.bsa_b200.fwd.default,
+                          (qc.detach(), kc.detach(), vc.detach(), ic, 0, nc, None, 0.088, 128, "bhsd"),
+                          test_utils=("test_schema", "test_faketensor"))
+
+
 def test_host_pipeline_matches_direct_calls():
     """pinned host tensors in, pinned host tensors out, head chunks pipelined over three streams."""
     from block_sparse_attention import HostPipeline, bsa_attn_bwd, bsa_attn_fwd

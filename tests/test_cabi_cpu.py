@@ -101,3 +101,21 @@ def test_policies_and_public_names():
     sig = inspect.signature(bsa.bsa_attn_fwd)
     assert list(sig.parameters)[:6] == ["q", "k", "v", "q2k_block_index", "block_sparse_num", "block_sizes"]
     assert sig.parameters["sparse_block_size"].default == 64 and sig.parameters["kv_splits"].default == 1
+
+
+def test_custom_ops_trace_with_fake_tensors_on_cpu():
+    """torch.ops.bsa_b200.fwd has a shape-only implementation: a graph can be traced without a GPU."""
+    import torch
+    from torch._subclasses.fake_tensor import FakeTensorMode
+    from block_sparse_attention import block_sparse_attention_op
+    with FakeTensorMode():
+        q = torch.empty(2, 4, 512, 128, dtype=torch.bfloat16, device="cuda")
+        k = torch.empty(2, 4, 768, 128, dtype=torch.bfloat16, device="cuda")
+        idx = torch.empty(2, 4, 4, 3, dtype=torch.int32, device="cuda")
+        out = block_sparse_attention_op(q, k, k, idx, 3)
+        assert out.shape == q.shape and out.dtype == torch.bfloat16
+        o2, lse = torch.ops.bsa_b200.fwd(q.transpose(1, 2), k.transpose(1, 2), k.transpose(1, 2), idx, 3, None, None,
+                                         0.1, 128, "bshd")
+        assert o2.shape == (2, 512, 4, 128) and lse.shape == (2, 4, 512) and lse.dtype == torch.float32
+        dq, dk, dv = torch.ops.bsa_b200.bwd(out, q, k, k, out, lse, idx, 3, None, None, 0.1, 128, "bhsd")
+        assert dq.shape == q.shape and dk.shape == k.shape and dv.shape == k.shape
