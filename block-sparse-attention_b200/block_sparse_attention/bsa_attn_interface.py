@@ -276,7 +276,8 @@ def bsa_attn_fwd(
     (``count`` = ``q2k_block_nums[b,h,m]`` or ``block_sparse_num``), ``block_sizes`` masks the tail tokens
     of KV blocks, rows with no live block give ``out = 0`` and ``lse = -inf``, LSE is the natural log of
     the scaled scores' partition sum and is returned iff ``return_lse``, a gradient is required or an
-    ``lse`` buffer was passed.  BF16 only, D = 128.  Relaxations over the reference: odd fixed counts are
+    ``lse`` buffer was passed.  BF16 (FP16 with 128-token blocks); D = 128, or 64 / 96 with 128-token blocks
+    (those ride on the 128-wide tiles: the tensor maps zero-fill the missing channels).  Relaxations over the reference: odd fixed counts are
     accepted for 128-token blocks and the physical KV tail is always masked.
     """
     assert sparse_block_size in (64, 128), f"sparse_block_size must be 64 or 128, got {sparse_block_size}"
@@ -306,7 +307,11 @@ def bsa_attn_fwd(
     B, Hq, Sq, D = qb.shape
     Bk, Hkv, Sk, Dk = kb.shape
     assert vb.shape == kb.shape and Bk == B and Dk == D
-    assert D == 128, "head dimension must be 128"
+    if blk == 128:
+        # same set as the reference's 128-token forward (csrc/fwd/sm100_blk128/bsa_fwd_sm100.py:75-78)
+        assert D in (64, 96, 128), f"head dimension must be 64, 96 or 128 for sparse_block_size=128, got {D}"
+    else:
+        assert D == 128, "sparse_block_size=64 requires head dimension 128"
     assert Hq % Hkv == 0
     G = Hq // Hkv
     if blk == 64:
@@ -611,7 +616,12 @@ def bsa_attn_bwd(
     Bk, Hk, Sk, Dk = kb.shape
     assert Hk == H, "bwd does not support GQA/MQA"
     assert Bk == B and vb.shape == kb.shape and Dk == D
-    assert D == 128, f"bwd only supports head_dim=128, got {D}"
+    if D == 64:
+        # the reference's rule (bsa_attn_interface.py:3867-3873): a 64-wide head needs the 128-token path
+        assert blk == 128, ("head_dim=64 bwd only supports the 128-token path; pass q2k_block_index sized to "
+                            "sparse_block_size=128")
+    else:
+        assert D == 128, f"bwd only supports head_dim in {{64, 128}}, got {D}"
     assert ob.shape == qb.shape and dob.shape == qb.shape
     assert lse.shape == (B, H, Sq)
     device = q.device

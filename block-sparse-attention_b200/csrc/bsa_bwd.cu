@@ -57,6 +57,7 @@ struct BwdParams {
   long long idx_cap;  // entries per (b,h) of csr_indices
   int fixed_count, cap;
   int B, H, Sq, Sk, Nq, Nkv, G;
+  int D;  // head dimension (64 or 128): a 64-wide head rides on the 128-wide tiles, the tensor maps zero-fill
   float scale_log2, softmax_scale;
 };
 
@@ -70,7 +71,7 @@ __global__ void __launch_bounds__(256)
 bwd_preprocess_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ d_o,
                       const float* __restrict__ lse, float* __restrict__ lse_log2, float* __restrict__ delta,
                       long long os_b, long long os_h, long long os_s, long long ds_b, long long ds_h, long long ds_s,
-                      int H, int Sq, int SqPad, long long rows_pad) {
+                      int H, int Sq, int SqPad, long long rows_pad, int D) {
   const long long row0 = ((long long)blockIdx.x * 8 + (threadIdx.x >> 5)) * kPreRowsPerWarp;
   if (row0 >= rows_pad) return;
   const int lane = threadIdx.x & 31;
@@ -88,7 +89,7 @@ bwd_preprocess_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* 
     const int s = s0 + 2 * i + sub;
     ov[i] = make_uint4(0, 0, 0, 0);
     dv[i] = make_uint4(0, 0, 0, 0);
-    if (s < Sq) {
+    if (s < Sq && chunk * 8 < D) {
       ov[i] = *reinterpret_cast<const uint4*>(o_base + (long long)s * os_s);
       dv[i] = *reinterpret_cast<const uint4*>(d_base + (long long)s * ds_s);
     }
@@ -425,7 +426,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const int seq = m * BLK + row;
       __nv_bfloat16* dq_row = p.dq + b * p.dq_stride[0] + h * p.dq_stride[1] + (long long)seq * p.dq_stride[2] + grp * 64;
       if (n == 0) {
-        if (row_active && seq < p.Sq) {
+        if (row_active && seq < p.Sq && grp * 64 < p.D) {
 #pragma unroll
           for (int ch = 0; ch < 8; ++ch) reinterpret_cast<uint4*>(dq_row)[ch] = make_uint4(0, 0, 0, 0);
         }
@@ -515,7 +516,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
       tc_fence_before();
       mbar_arrive(BAR(kDqFree));
-      if (row_active && seq < p.Sq) store_row_half(dq_row, acc, p.softmax_scale);
+      if (row_active && seq < p.Sq && grp * 64 < p.D) store_row_half(dq_row, acc, p.softmax_scale);
       PT_MARK(5)
     }
     if ((warp & 3) == 0) { PTB_FLUSH(grp * 8) }
@@ -806,7 +807,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const uint32_t base = r_cnt;
       r_cnt += 2 * T;
       const int kv = nb * BLK + row;
-      const bool kv_valid = row_active && kv < p.Sk;                   // this thread stores a dK / dV row
+      const bool kv_valid = row_active && kv < p.Sk && grp * 64 < p.D;  // this thread stores a dK / dV row half
       const bool kv_live = row < bwd_block_len<BLK>(p, b, h, nb);       // the token takes part in the softmax
       __nv_bfloat16* dk_row = p.dk + b * p.dk_stride[0] + h * p.dk_stride[1] + (long long)kv * p.dk_stride[2] + grp * 64;
       __nv_bfloat16* dv_row = p.dv + b * p.dv_stride[0] + h * p.dv_stride[1] + (long long)kv * p.dv_stride[2] + grp * 64;
@@ -962,7 +963,8 @@ extern "C" int64_t bsa_bwd_workspace_bytes(int32_t B, int32_t H, int32_t Sq, int
 extern "C" int bsa_bwd(const bsa_bwd_args* a, void* cuda_stream) {
   if (!a) return set_error(BSA_ERR_INVALID, "bsa_bwd: null args");
   if (a->blk != 128 && a->blk != 64) return set_error(BSA_ERR_UNSUPPORTED, "bsa_bwd: block size %d not built (64 or 128)", a->blk);
-  if (a->D != 128) return set_error(BSA_ERR_UNSUPPORTED, "bsa_bwd: head dimension %d not built (128 only)", a->D);
+  if (a->D != 128 && !(a->D == 64 && a->blk == 128))
+    return set_error(BSA_ERR_UNSUPPORTED, "bsa_bwd: head dimension %d not built (128, or 64 with 128-token blocks)", a->D);
   if (a->B < 1 || a->H < 1 || a->Sq < 1 || a->Sk < 1) return set_error(BSA_ERR_INVALID, "bsa_bwd: non-positive extent");
   if (!a->dout || !a->q || !a->k || !a->v || !a->out || !a->lse || !a->dq || !a->dk || !a->dv || !a->q2k_index ||
       !a->csr_offsets || !a->csr_indices || !a->workspace || !a->status)
@@ -988,14 +990,14 @@ extern "C" int bsa_bwd(const bsa_bwd_args* a, void* cuda_stream) {
   bwd_preprocess_kernel<<<(unsigned)((rows_pad + 8 * kPreRowsPerWarp - 1) / (8 * kPreRowsPerWarp)), 256, 0, st>>>(
       reinterpret_cast<const __nv_bfloat16*>(a->out), reinterpret_cast<const __nv_bfloat16*>(a->dout), a->lse, lse_log2,
       delta, a->o_stride[0], a->o_stride[1], a->o_stride[2], a->do_stride[0], a->do_stride[1], a->do_stride[2], a->H,
-      a->Sq, Nq * blk, rows_pad);
+      a->Sq, Nq * blk, rows_pad, a->D);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "bwd preprocess launch: %s", cudaGetErrorString(e));
 
   CUtensorMap tq, tdo, tk, tv;
   {
-    uint64_t qd[4] = {128, (uint64_t)a->Sq, (uint64_t)a->H, (uint64_t)a->B};
-    uint64_t kd[4] = {128, (uint64_t)a->Sk, (uint64_t)a->H, (uint64_t)a->B};
+    uint64_t qd[4] = {(uint64_t)a->D, (uint64_t)a->Sq, (uint64_t)a->H, (uint64_t)a->B};
+    uint64_t kd[4] = {(uint64_t)a->D, (uint64_t)a->Sk, (uint64_t)a->H, (uint64_t)a->B};
     uint32_t box[4] = {64, (uint32_t)blk, 1, 1};
     auto strides = [](const int64_t* s, uint64_t* out) {
       out[0] = (uint64_t)s[2] * 2;
@@ -1043,6 +1045,7 @@ extern "C" int bsa_bwd(const bsa_bwd_args* a, void* cuda_stream) {
   p.Nq = Nq;
   p.Nkv = Nkv;
   p.G = a->num_q_groups;
+  p.D = a->D;
   p.softmax_scale = a->softmax_scale;
   p.scale_log2 = a->softmax_scale * kLog2e;
 

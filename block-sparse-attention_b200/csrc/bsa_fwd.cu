@@ -60,6 +60,7 @@ struct FwdParams {
   int fixed_count, cap;
   int B, Hq, Hkv, G, Hidx, packed;
   int Sq, Sk, NqT, Nkv;
+  int D;  // head dimension (64, 96 or 128): narrower heads ride on the 128-wide tiles, the tensor maps zero-fill
   int splits;
   int f16;  // 16-bit inputs are IEEE half instead of bfloat16 (128-token blocks, unsplit only)
   int num_work;  // B * Hidx * NqT * splits
@@ -71,6 +72,10 @@ struct FwdParams {
 // 2 -> 3.97 ms, 4 -> 4.30 ms: the kernel is bound by its dependency chain, not by the SFU, so it is off.
 #ifndef BSA_EX2_EMU8
 #define BSA_EX2_EMU8 0
+#endif
+// Same idea for the e4m3 path, counted in pairs out of four.
+#ifndef BSA_EX2_EMU_FP8
+#define BSA_EX2_EMU_FP8 0
 #endif
 
 constexpr int kThreads = 384;
@@ -705,10 +710,20 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
                 const uint64_t sc2 = pack2(sc, sc);
                 unpack2(ffma2(pack2(sv[c], sv[c + 1]), sc2, nm2), x0, x1);
                 unpack2(ffma2(pack2(sv[c + 2], sv[c + 3]), sc2, nm2), x2, x3);
-                x0 = ex2_approx(x0);
-                x1 = ex2_approx(x1);
-                x2 = ex2_approx(x2);
-                x3 = ex2_approx(x3);
+                // e4m3 packing shares the special-function pipe with ex2, which bounds this loop: a share of
+                // the exponentials takes the polynomial on the FMA pipe instead
+                if (((2 * e) & 3) < BSA_EX2_EMU_FP8) {
+                  unpack2(ex2_emu2(x0, x1), x0, x1);
+                } else {
+                  x0 = ex2_approx(x0);
+                  x1 = ex2_approx(x1);
+                }
+                if (((2 * e + 1) & 3) < BSA_EX2_EMU_FP8) {
+                  unpack2(ex2_emu2(x2, x3), x2, x3);
+                } else {
+                  x2 = ex2_approx(x2);
+                  x3 = ex2_approx(x3);
+                }
               }
               s0 = fadd2(s0, pack2(x0, x1));
               s1 = fadd2(s1, pack2(x2, x3));
@@ -881,7 +896,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         // next tile may overwrite them
         ok = mbar_rendezvous_poll(BAR(kGrpB), grp_b, wctx, 323);
         if (!ok) break;
-        if (issuer) {
+        if (issuer && grp * 64 < p.D) {  // a 64-wide head has no second column slab to store
           const int cs = t.m * seq_per_tile;
           tma_store_5d(&tm_o, smem_u32(sO + grp * (128 * 128)), grp * 64, t.g, cs, t.hkv, t.b);
           tma_store_commit();
@@ -938,7 +953,10 @@ using namespace bsa;
 extern "C" int bsa_fwd(const bsa_fwd_args* a, void* cuda_stream) {
   if (!a) return set_error(BSA_ERR_INVALID, "bsa_fwd: null args");
   if (a->blk != 64 && a->blk != 128) return set_error(BSA_ERR_INVALID, "bsa_fwd: blk must be 64 or 128");
-  if (a->D != 128) return set_error(BSA_ERR_UNSUPPORTED, "bsa_fwd: head dimension %d not built (128 only)", a->D);
+  if (a->D != 128 && a->D != 96 && a->D != 64)
+    return set_error(BSA_ERR_UNSUPPORTED, "bsa_fwd: head dimension %d not built (64, 96 or 128)", a->D);
+  if (a->D != 128 && (a->blk != 128 || a->splits != 1 || a->dtype == BSA_DTYPE_E4M3))
+    return set_error(BSA_ERR_UNSUPPORTED, "bsa_fwd: head dimensions below 128 are built for unsplit 16-bit 128-token blocks");
   if (a->dtype != BSA_DTYPE_BF16 && a->dtype != BSA_DTYPE_E4M3 && a->dtype != BSA_DTYPE_F16)
     return set_error(BSA_ERR_INVALID, "bsa_fwd: unknown dtype %d", a->dtype);
   if (a->dtype == BSA_DTYPE_F16 && (a->blk != 128 || a->splits != 1))
@@ -992,6 +1010,7 @@ extern "C" int bsa_fwd(const bsa_fwd_args* a, void* cuda_stream) {
   const long long rows = packed ? (long long)a->Sq * G : a->Sq;
   p.NqT = (int)((rows + a->blk - 1) / a->blk);
   p.Nkv = (a->Sk + a->blk - 1) / a->blk;
+  p.D = a->D;
   p.splits = a->splits;
   p.f16 = a->dtype == BSA_DTYPE_F16;
   const long long work = (long long)p.B * p.Hidx * p.NqT * p.splits;
@@ -1007,7 +1026,8 @@ extern "C" int bsa_fwd(const bsa_fwd_args* a, void* cuda_stream) {
   const uint32_t inner = 128 / elt;  // elements per 128-byte swizzle row
   CUtensorMap tq, tk, tv, to;
   {
-    uint64_t dims[5] = {128, (uint64_t)G, (uint64_t)a->Sq, (uint64_t)a->Hkv, (uint64_t)a->B};
+    // the innermost extent is the true head dimension: boxes that reach beyond it read zeros / are clipped
+    uint64_t dims[5] = {(uint64_t)a->D, (uint64_t)G, (uint64_t)a->Sq, (uint64_t)a->Hkv, (uint64_t)a->B};
     uint64_t str[4] = {(uint64_t)a->q_stride[1] * elt, (uint64_t)a->q_stride[2] * elt,
                        (uint64_t)a->q_stride[1] * G * elt, (uint64_t)a->q_stride[0] * elt};
     uint32_t box[5] = {inner, packed ? (uint32_t)G : 1u, (uint32_t)(packed ? a->blk / G : a->blk), 1, 1};
@@ -1024,7 +1044,7 @@ extern "C" int bsa_fwd(const bsa_fwd_args* a, void* cuda_stream) {
     }
   }
   {
-    uint64_t dims[4] = {128, (uint64_t)a->Sk, (uint64_t)a->Hkv, (uint64_t)a->B};
+    uint64_t dims[4] = {(uint64_t)a->D, (uint64_t)a->Sk, (uint64_t)a->Hkv, (uint64_t)a->B};
     uint64_t kstr[3] = {(uint64_t)a->k_stride[2] * elt, (uint64_t)a->k_stride[1] * elt,
                         (uint64_t)a->k_stride[0] * elt};
     uint64_t vstr[3] = {(uint64_t)a->v_stride[2] * elt, (uint64_t)a->v_stride[1] * elt,

@@ -65,6 +65,9 @@ int bsa_num_sms(int device);
  * [splits, B, Hq, Sq, D] and its log-sum-exp to partial_lse [splits, B, Hq, Sq]; `out`/`lse` are not
  * touched and the caller runs bsa_fwd_combine afterwards.
  *
+ * D = 128; with 16-bit inputs, 128-token blocks and splits = 1 also D = 64 and 96, the head dimensions of the
+ * reference's 128-token forward (csrc/fwd/sm100_blk128/bsa_fwd_sm100.py:75-78).
+ *
  * work_order: the persistent CTAs walk the tile rows in this order (CTA c takes entries c, 2G-1-c, 2G+c, ...
  * of it, G = grid size); a longest-first order balances skewed per-row counts.  NULL = natural order.
  *
@@ -213,7 +216,8 @@ int bsa_build_k2q_csr(const int32_t* q2k_index, const int32_t* q2k_nums, int32_t
                       void* cuda_stream);
 
 /*
- * Backward pass, BF16, MHA, D = 128, blk = 128 or 64 tokens: dQ, dK, dV from dO, Q, K, V, O, LSE.
+ * Backward pass, BF16, MHA, D = 128 (or 64 with blk = 128), blk = 128 or 64 tokens: dQ, dK, dV from dO, Q, K,
+ * V, O, LSE.
  * Replaces the preprocess / main / postprocess callables of
  * csrc/bwd/sm100_blk128/bsa_bwd_sm100.py:2178-2385 (blk128) and of the blk64 driver
  * bsa_attn_interface.py:4022-4290 over csrc/bwd/sm100_blk64/bsa_bwd_sm100.py (preprocess

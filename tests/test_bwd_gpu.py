@@ -202,6 +202,28 @@ def test_128_token_blocks_honour_block_sizes_like_the_forward():
     _check(got, q, k, v, do, bias, 1 / math.sqrt(128))
 
 
+def test_head_dimension_64_with_128_token_blocks():
+    """D = 64 backward exists on the 128-token path only (bsa_attn_interface.py:3867-3873)."""
+    from block_sparse_attention import bsa_attn_bwd, bsa_attn_fwd
+    gen = torch.Generator().manual_seed(64)
+    B, H, Sq, Sk, D = 1, 3, 300, 520, 64
+    q, do = (torch.randn(B, H, Sq, D, generator=gen).bfloat16() for _ in range(2))
+    k, v = (torch.randn(B, H, Sk, D, generator=gen).bfloat16() for _ in range(2))
+    Nq, Nkv = 3, 5
+    index = torch.stack([torch.randperm(Nkv, generator=gen) for _ in range(B * H * Nq)]).int().reshape(B, H, Nq, Nkv)
+    nums = torch.tensor([[[2, 0, 5], [1, 3, 4], [5, 5, 1]]], dtype=torch.int32)
+    qc, kc, vc, doc, ic, nc = (t.cuda() for t in (q, k, v, do, index, nums))
+    out, lse = bsa_attn_fwd(qc, kc, vc, ic, 0, q2k_block_nums=nc, return_lse=True, sparse_block_size=128)
+    got = bsa_attn_bwd(doc, qc, kc, vc, out, lse, ic, 0, q2k_block_nums=nc, sparse_block_size=128)
+    assert got[0].shape == q.shape and got[1].shape == k.shape
+    sizes = torch.tensor([128, 128, 128, 128, Sk - 512], dtype=torch.int32)
+    bias = orc.block_sparse_to_attn_bias(index, 0, sizes, Sq, Sk, q2k_block_nums=nums)
+    _check(tuple(t.float().cpu() for t in got), q, k, v, do, bias, 1 / math.sqrt(D))
+    with pytest.raises(AssertionError):
+        bsa_attn_bwd(doc, qc, kc, vc, out, lse, torch.zeros(B, H, 5, 9, dtype=torch.int32, device="cuda"), 1,
+                     sparse_block_size=64)
+
+
 def test_argument_errors():
     from block_sparse_attention import bsa_attn_bwd
     x = torch.zeros(1, 2, 128, 128, device="cuda").bfloat16()

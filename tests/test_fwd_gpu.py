@@ -320,3 +320,30 @@ def test_float16_inputs_128_token_blocks():
     _check(out, lse, ref_out, ref_lse, qh, kh, vh)
     with pytest.raises(AssertionError):
         _fwd(qh.cuda()[:, :2], kh.cuda(), vh.cuda(), index.cuda()[:, :2, :, :4].contiguous(), 2, sparse_block_size=64)
+
+
+@pytest.mark.parametrize("D", [64, 96])
+def test_head_dimensions_below_128_with_128_token_blocks(D):
+    """the reference's 128-token forward also takes 64- and 96-wide heads (bsa_fwd_sm100.py:75-78)."""
+    gen = torch.Generator().manual_seed(D)
+    B, Hq, Hkv, Sq, Sk = 2, 4, 2, 300, 700
+    q = torch.randn(B, Hq, Sq, D, generator=gen).bfloat16()
+    k = torch.randn(B, Hkv, Sk, D, generator=gen).bfloat16()
+    v = torch.randn(B, Hkv, Sk, D, generator=gen).bfloat16()
+    Nq, Nkv = 3, 6
+    index = torch.stack([torch.randperm(Nkv, generator=gen) for _ in range(B * Hq * Nq)]).int().reshape(B, Hq, Nq, Nkv)
+    nums = torch.randint(0, Nkv + 1, (B, Hq, Nq), generator=gen, dtype=torch.int32)
+    out, lse = _fwd(*_cuda(q, k, v, index), 0, q2k_block_nums=nums.cuda(), return_lse=True, sparse_block_size=128,
+                    pack_gqa=False)
+    assert out.shape == q.shape
+    ref_out, ref_lse = orc.attention_gathered(q, k, v, index, 0, nums=nums)
+    _check(out, lse, ref_out, ref_lse, q, k, v)
+    # BSHD layout with a supplied buffer, fixed count
+    qs, ks, vs = (t.transpose(1, 2).contiguous() for t in (q, k, v))
+    buf = torch.full(qs.shape, 3.0, dtype=torch.bfloat16, device="cuda")
+    out2, _ = _fwd(*_cuda(qs, ks, vs, index), 2, layout="bshd", out=buf, return_lse=True, sparse_block_size=128,
+                   pack_gqa=False)
+    ref2, _ = orc.attention_gathered(q, k, v, index, 2)
+    assert (out2.transpose(1, 2).float().cpu() - ref2).abs().max().item() < 3e-2
+    with pytest.raises(AssertionError):
+        _fwd(*_cuda(q[:, :2], k, v, index[:, :2].contiguous()), 2, sparse_block_size=64)   # 64-token blocks need D = 128
