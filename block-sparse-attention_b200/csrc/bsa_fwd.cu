@@ -343,7 +343,6 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint32_t ring_first = s ? (uint32_t)Cfg::kRing0 : 0u;
     bool ok = true;
     uint32_t turn_cnt = 0;      // completed waits on this issuer's turn barrier
-    int prev_last_stream = -1;  // stream that issued the last batch of the previous non-empty tile
     auto turn_wait = [&]() -> bool {
       const bool r = mbar_wait(turn_base + 8u * s, turn_cnt & 1, wctx, 205);
       ++turn_cnt;
@@ -440,27 +439,29 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         return true;
       };
 
-      // turns of this tile: QK(0) [stream 0], QK(1) [stream 1, if it has work], then batch i = {PV(i),
-      // QK(i+2)} by stream i & 1.  A turn waits for the token only if its predecessor belongs to the other
-      // issuer, and passes it only if its successor does (the successor of the last batch is QK(0) of the
-      // next tile with work, a turn of stream 0).
+      // turns of this tile: QK(0) [stream 0], QK(1) [stream 1], then batch i = {PV(i), QK(i+2)} by stream
+      // i & 1.  Every turn but the first waits for the token of its predecessor and every turn but the last
+      // passes it on, so all passes are consumed inside the tile (tiles are ordered among themselves by the
+      // Q buffer: the next Q tile is loaded only after both issuers have finished this one).  Short rows
+      // are not worth the hand-offs: below kTurnMinIters iterations the issuers run freely.
+      constexpr int kTurnMinIters = 6;
+      const bool turns = n_it >= kTurnMinIters;
       if (s == 0) {
-        ok = issue_qk(0, prev_last_stream == 1);
-        if (ok && n_it >= 2) turn_pass();
+        ok = issue_qk(0, false);
+        if (ok && turns) turn_pass();
       } else if (n_it >= 2) {
-        ok = issue_qk(1, true);
-        if (ok) turn_pass();
+        ok = issue_qk(1, turns);
+        if (ok && turns) turn_pass();
       }
       for (int i = s; i < n_it && ok; i += 2) {
-        ok = issue_pv(i, i >= 1 || n_it >= 2);
+        ok = issue_pv(i, turns);
         PT_TRACE(2 + s, 1)
         if (ok && i + 2 < n_it) ok = issue_qk(i + 2, false);
-        if (ok && (i + 1 < n_it || s == 1)) turn_pass();
+        if (ok && turns && i + 1 < n_it) turn_pass();
         PT_TRACE(2 + s, 2)
         PT_TRACE_NEXT(2 + s)
       }
       if (!ok) break;
-      prev_last_stream = (n_it - 1) & 1;
       // Q is free once the QK MMAs of BOTH streams have completed: each issuer signals for its own MMAs
       // (a stream without work arrives directly; it cannot arrive twice in one phase because the next Q
       // tile, which it waits for first, is only loaded after this phase has completed).  O_s is final
