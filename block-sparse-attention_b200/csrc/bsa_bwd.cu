@@ -186,27 +186,29 @@ __device__ __forceinline__ uint64_t desc_mn_major(uint32_t saddr) { return umma_
 constexpr uint64_t kTileDescStep = kTile >> 4;  // descriptor distance between consecutive ring tiles
 
 // D = A(smem, K-major) * B(smem, K-major)^T over the 128-deep contraction: 8 k-steps across two slabs
-__device__ __forceinline__ void mma_ss_kk(uint32_t d, uint64_t a_desc, uint64_t b_desc, bool acc) {
+// All helpers are called by the whole (converged) issuing warp; only the lane with led != 0 issues.
+__device__ __forceinline__ void mma_ss_kk(uint32_t d, uint64_t a_desc, uint64_t b_desc, bool acc, uint32_t led) {
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     const uint64_t off = (uint64_t)((k >> 2) * (kSlab >> 4) + (k & 3) * 2);
-    umma_f16_ss(d, a_desc + off, b_desc + off, kIdescKK, (acc || k > 0) ? 1u : 0u);
+    umma_f16_ss_led(d, a_desc + off, b_desc + off, kIdescKK, (acc || k > 0) ? 1u : 0u, led);
   }
 }
 // D (+)= A(smem, K-major [rows][contraction]) * B(smem tile [contraction rows][128 channels], MN-major)
-__device__ __forceinline__ void mma_ss_kmn(uint32_t d, uint64_t a_desc, uint64_t b_desc_mn, bool acc) {
+__device__ __forceinline__ void mma_ss_kmn(uint32_t d, uint64_t a_desc, uint64_t b_desc_mn, bool acc, uint32_t led) {
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     const uint64_t aoff = (uint64_t)((k >> 2) * (kSlab >> 4) + (k & 3) * 2);
-    umma_f16_ss(d, a_desc + aoff, b_desc_mn + (uint64_t)(k * 128), kIdescKMN, (acc || k > 0) ? 1u : 0u);
+    umma_f16_ss_led(d, a_desc + aoff, b_desc_mn + (uint64_t)(k * 128), kIdescKMN, (acc || k > 0) ? 1u : 0u, led);
   }
 }
 // D (+)= A(tmem bf16, two 32-column halves at a_lo / a_hi) * B(smem MN-major)
-__device__ __forceinline__ void mma_ts_kmn(uint32_t d, uint32_t a_lo, uint32_t a_hi, uint64_t b_desc_mn, bool acc) {
+__device__ __forceinline__ void mma_ts_kmn(uint32_t d, uint32_t a_lo, uint32_t a_hi, uint64_t b_desc_mn, bool acc,
+                                           uint32_t led) {
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     const uint32_t a = (k < 4) ? (a_lo + (uint32_t)k * 8u) : (a_hi + (uint32_t)(k - 4) * 8u);
-    umma_f16_ts(d, a, b_desc_mn + (uint64_t)(k * 128), kIdescKMN, (acc || k > 0) ? 1u : 0u);
+    umma_f16_ts_led(d, a, b_desc_mn + (uint64_t)(k * 128), kIdescKMN, (acc || k > 0) ? 1u : 0u, led);
   }
 }
 
@@ -326,6 +328,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     uint32_t r_cnt = 0, q_cnt = 0, ds_cnt = 0, free_cnt = 0;
     bool ok = true;
     bool first_tile = true;
+    const uint32_t led = lane == 0;  // the whole warp runs the issue code, this lane issues
     const uint64_t dq_desc = desc_k_major(smem_u32(sQ)), ddo_desc = desc_k_major(smem_u32(sdO));
     const uint64_t ring_k = desc_k_major(smem_u32(sRing)), ring_mn = desc_mn_major(smem_u32(sRing));
     PT_DECL
@@ -349,9 +352,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       auto issue_s = [&](int j) -> bool {
         if (!wait_full(base + 2 * j)) return false;
         tc_fence_after();
-        if (lane == 0) {
-          mma_ss_kk(tS[j & 1], dq_desc, ring_k + stage_of(base + 2 * j) * kTileDescStep, false);
-          umma_commit(BAR(kSFull + (j & 1)));
+        {
+          mma_ss_kk(tS[j & 1], dq_desc, ring_k + stage_of(base + 2 * j) * kTileDescStep, false, led);
+          umma_commit_led(BAR(kSFull + (j & 1)), led);
         }
         __syncwarp();
         return true;
@@ -359,10 +362,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       auto issue_dp = [&](int j) -> bool {
         if (!wait_full(base + 2 * j + 1)) return false;
         tc_fence_after();
-        if (lane == 0) {
-          mma_ss_kk(tdP, ddo_desc, ring_k + stage_of(base + 2 * j + 1) * kTileDescStep, false);
-          umma_commit(BAR(kDpFull));
-          umma_commit(BAR(kREmpty + stage_of(base + 2 * j + 1)));  // V_j is only read by this MMA
+        {
+          mma_ss_kk(tdP, ddo_desc, ring_k + stage_of(base + 2 * j + 1) * kTileDescStep, false, led);
+          umma_commit_led(BAR(kDpFull), led);
+          umma_commit_led(BAR(kREmpty + stage_of(base + 2 * j + 1)), led);  // V_j is only read by this MMA
         }
         __syncwarp();
         return true;
@@ -384,12 +387,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           ++free_cnt;
         }
         tc_fence_after();
-        if (lane == 0) {
+        {
           const uint32_t sk = stage_of(base + 2 * j);
           // dQ += dS_j (bf16 in tensor memory, at the head of each group's half of the dP columns) * K_j
           // (MN-major view of the K tile)
-          mma_ts_kmn(tdQ, tdP, tdP + 64u, ring_mn + sk * kTileDescStep, j > 0);
-          umma_commit(BAR(kREmpty + sk));
+          mma_ts_kmn(tdQ, tdP, tdP + 64u, ring_mn + sk * kTileDescStep, j > 0, led);
+          umma_commit_led(BAR(kREmpty + sk), led);
         }
         __syncwarp();
         if (j + 1 < n) {
@@ -399,9 +402,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         if (j + 2 < n) ok = issue_s(j + 2);
       }
       if (!ok) break;
-      if (lane == 0) {
-        umma_commit(BAR(kDqFinal));
-        umma_commit(BAR(kQEmpty));
+      {
+        umma_commit_led(BAR(kDqFinal), led);
+        umma_commit_led(BAR(kQEmpty), led);
       }
       __syncwarp();
       r_cnt += 2 * n;
@@ -684,6 +687,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     // Each issuer visits every ring position in increasing order (a parity wait is never more than one
     // phase behind) and every ring stage is released by one commit of each issuer.
     const int who = warp - kBwdMmaWarp;
+    const uint32_t led = lane == 0;  // the whole warp runs the issue code, this lane issues
     uint32_t r_cnt = 0, kv_cnt = 0, in_cnt = 0, free_cnt = 0;
     bool ok = true, first_item = true;
     const uint64_t k_desc = desc_k_major(smem_u32(sK)), v_desc = desc_k_major(smem_u32(sV));
@@ -708,10 +712,10 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (who == 0) {
         // ---- issuer 0
         ok = wait_full(base);
-        if (ok && lane == 0) {
-          mma_ss_kk(tS, k_desc, ring_k + stage_of(base) * kTileDescStep, false);  // S^T_0
-          umma_commit(BAR(kSFull));
-          umma_commit(BAR(kREmpty + stage_of(base)));
+        if (ok) {
+          mma_ss_kk(tS, k_desc, ring_k + stage_of(base) * kTileDescStep, false, led);  // S^T_0
+          umma_commit_led(BAR(kSFull), led);
+          umma_commit_led(BAR(kREmpty + stage_of(base)), led);
         }
         __syncwarp();
         for (int i = 0; i < T && ok; ++i) {
@@ -728,20 +732,20 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
           if (i == 0 && !first_item) ++free_cnt;
           tc_fence_after();
-          if (lane == 0) {
+          {
             const uint32_t sd = stage_of(base + 2 * i + 1);
-            mma_ts_kmn(tdV, tS, tS + 64u, ring_mn + sd * kTileDescStep, i > 0);  // dV += P^T dO_i
-            umma_commit(BAR(kREmpty + sd));
+            mma_ts_kmn(tdV, tS, tS + 64u, ring_mn + sd * kTileDescStep, i > 0, led);  // dV += P^T dO_i
+            umma_commit_led(BAR(kREmpty + sd), led);
           }
           __syncwarp();
           if (i + 1 < T) {
             ok = wait_full(base + 2 * i + 2);  // Q_{i+1}
             if (!ok) break;
-            if (lane == 0) {
+            {
               const uint32_t sq = stage_of(base + 2 * i + 2);
-              mma_ss_kk(tS, k_desc, ring_k + sq * kTileDescStep, false);  // S^T_{i+1}, after dV_i in program order
-              umma_commit(BAR(kSFull));
-              umma_commit(BAR(kREmpty + sq));
+              mma_ss_kk(tS, k_desc, ring_k + sq * kTileDescStep, false, led);  // S^T_{i+1}, after dV_i in program order
+              umma_commit_led(BAR(kSFull), led);
+              umma_commit_led(BAR(kREmpty + sq), led);
             }
             __syncwarp();
           }
@@ -752,12 +756,12 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           ok = wait_full(base + 2 * i);  // Q_i (needed for dK_i; visited first to keep the waits in order)
           if (ok) ok = wait_full(base + 2 * i + 1);  // dO_i
           if (!ok) break;
-          if (lane == 0) {
+          {
             const uint32_t sd = stage_of(base + 2 * i + 1);
             // dP^T_i: in program order after dK_{i-1}, which read dS^T_{i-1} from the same columns
-            mma_ss_kk(tdP, v_desc, ring_k + sd * kTileDescStep, false);
-            umma_commit(BAR(kDpFull));
-            umma_commit(BAR(kREmpty + sd));
+            mma_ss_kk(tdP, v_desc, ring_k + sd * kTileDescStep, false, led);
+            umma_commit_led(BAR(kDpFull), led);
+            umma_commit_led(BAR(kREmpty + sd), led);
           }
           __syncwarp();
           PT_MARK(0)
@@ -771,18 +775,18 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
           if (i == 0 && !first_item) ++free_cnt;
           tc_fence_after();
-          if (lane == 0) {
+          {
             const uint32_t sq = stage_of(base + 2 * i);
-            mma_ts_kmn(tdK, tdP, tdP + 64u, ring_mn + sq * kTileDescStep, i > 0);  // dK += dS^T Q_i
-            umma_commit(BAR(kREmpty + sq));
+            mma_ts_kmn(tdK, tdP, tdP + 64u, ring_mn + sq * kTileDescStep, i > 0, led);  // dK += dS^T Q_i
+            umma_commit_led(BAR(kREmpty + sq), led);
           }
           __syncwarp();
         }
       }
       if (!ok) break;
-      if (lane == 0) {  // both issuers: their share of the accumulators is final, K / V no longer needed
-        umma_commit(BAR(kFinal));
-        umma_commit(BAR(kKvEmpty));
+      {  // both issuers: their share of the accumulators is final, K / V no longer needed
+        umma_commit_led(BAR(kFinal), led);
+        umma_commit_led(BAR(kKvEmpty), led);
       }
       __syncwarp();
       r_cnt += 2 * T;
