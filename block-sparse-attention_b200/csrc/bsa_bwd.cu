@@ -166,9 +166,19 @@ __device__ __forceinline__ void store_row_half(__nv_bfloat16* dst, const uint32_
 #define BSA_BWD_EX2_EMU4 0
 #endif
 
+// 1 recomputes the probabilities with the packed half-precision exp2 (two results per special-function
+// operation).  Measured on B200 (cfg2 backward): 13.4 ms against 13.1 ms with the fp32 instruction - the
+// conversions to and from half precision cost what the unit saves, and the phase is bound by its tensor-memory
+// round trips (870 of its 1500 clocks remain with no exponential at all) - so it is off.
+#ifndef BSA_BWD_EX2_F16
+#define BSA_BWD_EX2_F16 0
+#endif
+
 // exp2 of two scaled-and-shifted scores (pair index `pair` selects the unit that computes them)
 __device__ __forceinline__ void exp2_pair(int pair, float x0, float x1, float& y0, float& y1) {
-  if ((pair & 3) < BSA_BWD_EX2_EMU4) {
+  if (BSA_BWD_EX2_F16) {
+    unpack_f16x2(ex2_f16x2(pack_f16x2(x0, x1)), y0, y1);
+  } else if ((pair & 3) < BSA_BWD_EX2_EMU4) {
     unpack2(ex2_emu2(x0, x1), y0, y1);
   } else {
     y0 = ex2_approx(x0);

@@ -482,6 +482,22 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
   return (uint32_t)lo | ((uint32_t)hi << 16);
 }
 
+// Two exponentials per special-function operation: 2^x on a packed pair of IEEE halves.  Measured on B200:
+// 17.4 clocks per four elements and scheduler (conversion included) against 32.0 for four ex2.approx.f32, i.e.
+// the special-function unit delivers 32 instead of 16 results per clock and SM.  The argument is rounded
+// to half precision first: relative error of the result <= |x| * 2^-11 * ln 2 (0.27 % at |x| = 8), the
+// size of the bf16 rounding the probabilities undergo anyway; arguments below -65504 give exactly 0.
+__device__ __forceinline__ uint32_t ex2_f16x2(uint32_t h2) {
+  uint32_t y;
+  asm("ex2.approx.f16x2 %0, %1;" : "=r"(y) : "r"(h2));
+  return y;
+}
+__device__ __forceinline__ void unpack_f16x2(uint32_t h2, float& lo, float& hi) {
+  asm("{\n\t.reg .f16 a, b;\n\tmov.b32 {a, b}, %2;\n\tcvt.f32.f16 %0, a;\n\tcvt.f32.f16 %1, b;\n\t}"
+      : "=f"(lo), "=f"(hi)
+      : "r"(h2));
+}
+
 // three-input maximum (one instruction on sm_100)
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
