@@ -225,9 +225,24 @@ __device__ __forceinline__ void mma_ts_kmn(uint32_t d, uint32_t a_lo, uint32_t a
 // ------------------------------------------------------------------------------------------------
 // 2. dQ kernel
 // ------------------------------------------------------------------------------------------------
-// smem: Q | dO | ring of 5 tiles (K_j, V_j alternating) | barriers | misc
-constexpr int kDqStages = 5;
-constexpr int kDqSmem = 2 * kTile + kDqStages * kTile + BwdSmem::kBarBytes + BwdSmem::kMisc;
+// smem: one ring of 7 tiles | barriers | misc.  Per query tile the ring carries Q, dO, K_0, V_0, K_1, V_1, ...
+// Q and dO only land there: the compute warps move them into tensor memory once per tile (thread = row), so the
+// S and dP MMAs read their stationary operand from tensor memory, the two stages go straight back to the ring,
+// and K / V tiles are prefetched three to four stages ahead.
+// Tensor memory: S @0, dP @128 (dS overwrites the head of each group's half), dQ @256, Q @384, dO @448.
+// S is single-buffered: S_{j+1} is issued as soon as every compute thread has loaded S_j into registers, i.e.
+// it runs under the exponentials of iteration j.
+constexpr int kDqStages = 7;
+constexpr int kDqSmem = kDqStages * kTile + BwdSmem::kBarBytes + BwdSmem::kMisc;
+
+// D = A(tmem bf16, 64 columns: rows = lanes, contraction packed two per column) * B(smem, K-major)^T
+__device__ __forceinline__ void mma_ts_kk(uint32_t d, uint32_t a_tmem, uint64_t b_desc, bool acc, uint32_t led) {
+#pragma unroll
+  for (int k = 0; k < 8; ++k) {
+    const uint64_t off = (uint64_t)((k >> 2) * (kSlab >> 4) + (k & 3) * 2);
+    umma_f16_ts_led(d, a_tmem + (uint32_t)k * 8u, b_desc + off, kIdescKK, (acc || k > 0) ? 1u : 0u, led);
+  }
+}
 
 // BLK = 64: the query tile has 64 rows (top half of the 128-row MMAs, lanes 64-127 idle) and one KV iteration
 // gathers two 64-token blocks into a 128-token tile (an odd count re-loads the last block as a masked phantom);
@@ -238,9 +253,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
               const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const BwdParams p) {
   constexpr int NS = kDqStages;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* sQ = smem_raw;
-  uint8_t* sdO = sQ + kTile;
-  uint8_t* sRing = sdO + kTile;
+  uint8_t* sRing = smem_raw;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sRing + NS * kTile);
   uint32_t& s_tmem_base = *reinterpret_cast<uint32_t*>(bars + 32);
   volatile int& s_abort = *reinterpret_cast<volatile int*>(bars + 33);
@@ -250,22 +263,22 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   }
   const uint32_t bar_base = smem_u32(bars);
   auto BAR = [&](int i) { return bar_base + (uint32_t)i * 8u; };
-  // q_full, q_empty, ring_full[NS], ring_empty[NS], s_full[2], dp_full, ds_full, dq_final, dq_free
-  constexpr int kQFull = 0, kQEmpty = 1, kRFull = 2, kREmpty = 2 + NS, kSFull = 2 + 2 * NS, kDpFull = kSFull + 2,
-                kDsFull = kDpFull + 1, kDqFinal = kDsFull + 1, kDqFree = kDqFinal + 1, kNumBars = kDqFree + 1;
+  // ring_full[NS], ring_empty[NS], s_full, s_free, dp_full, ds_full, dq_final, dq_free, q_tmem
+  constexpr int kRFull = 0, kREmpty = NS, kSFull = 2 * NS, kSFree = kSFull + 1, kDpFull = kSFree + 1,
+                kDsFull = kDpFull + 1, kDqFinal = kDsFull + 1, kDqFree = kDqFinal + 1, kQTmem = kDqFree + 1,
+                kNumBars = kQTmem + 1;
   static_assert(kNumBars <= 32, "barrier slots");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   WaitCtx wctx{&s_abort, p.status};
   if (threadIdx.x == 0) {
     s_abort = 0;
-    mbar_init(BAR(kQFull), 1);
-    mbar_init(BAR(kQEmpty), 1);
     for (int i = 0; i < NS; ++i) {
       mbar_init(BAR(kRFull + i), 1);
       mbar_init(BAR(kREmpty + i), 1);
     }
     mbar_init(BAR(kSFull), 1);
-    mbar_init(BAR(kSFull + 1), 1);
+    mbar_init(BAR(kSFree), 256);   // every compute thread has loaded its part of S_j: S_{j+1} may overwrite it
+    mbar_init(BAR(kQTmem), 256);   // Q and dO of the tile are in tensor memory
     mbar_init(BAR(kDpFull), 1);
     mbar_init(BAR(kDsFull), 256);
     mbar_init(BAR(kDqFinal), 1);
@@ -281,8 +294,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = s_tmem_base;
-  const uint32_t tS[2] = {tmem, tmem + 128u};
-  const uint32_t tdP = tmem + 256u, tdQ = tmem + 384u;
+  const uint32_t tS = tmem, tdP = tmem + 128u, tdQ = tmem + 256u, tQ = tmem + 384u, tdO = tmem + 448u;
   const int num_work = p.B * p.H * p.Nq;
 
   constexpr int kPerIt = 128 / BLK;               // KV blocks per 128-token iteration
@@ -292,9 +304,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     return max(0, min(c, p.cap));
   };
   auto iterations = [&](int count) { return (count + kPerIt - 1) / kPerIt; };
+  // ring positions of a tile with n iterations: Q, dO, then K_j at +2+2j and V_j at +3+2j
 
   if (warp == kBwdLoadWarp) {
-    uint32_t r_cnt = 0, q_cnt = 0;
+    uint32_t r_cnt = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
       const int cnt = row_count(w);
@@ -304,15 +317,17 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const int h = (w / p.Nq) % p.H;
       const int b = w / (p.Nq * p.H);
       const int32_t* row = p.q2k_index + (long long)w * p.cap;
-      ok = mbar_wait(BAR(kQEmpty), (q_cnt & 1) ^ 1, wctx, 400);
-      if (!ok) break;
-      ++q_cnt;
-      if (lane == 0) {
-        mbar_arrive_expect_tx(BAR(kQFull), 2 * kQBytes);
-        for (int sl = 0; sl < 2; ++sl) {
-          tma_load_4d(smem_u32(sQ + sl * kSlab), &tm_q, BAR(kQFull), sl * 64, m * BLK, h, b);
-          tma_load_4d(smem_u32(sdO + sl * kSlab), &tm_do, BAR(kQFull), sl * 64, m * BLK, h, b);
+      for (int which = 0; which < 2 && ok; ++which) {  // Q, dO
+        const uint32_t stage = r_cnt % NS, ph = (r_cnt / NS) & 1;
+        ok = mbar_wait(BAR(kREmpty + stage), ph ^ 1, wctx, 400);
+        if (!ok) break;
+        if (lane == 0) {
+          mbar_arrive_expect_tx(BAR(kRFull + stage), kQBytes);
+          const CUtensorMap* tm = which ? &tm_do : &tm_q;
+          for (int sl = 0; sl < 2; ++sl)
+            tma_load_4d(smem_u32(sRing + stage * kTile + sl * kSlab), tm, BAR(kRFull + stage), sl * 64, m * BLK, h, b);
         }
+        ++r_cnt;
       }
       for (int j = 0; j < n && ok; ++j) {
         const int blk0 = row[kPerIt * j];
@@ -335,23 +350,28 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       }
     }
   } else if (warp == kBwdMmaWarp) {
-    uint32_t r_cnt = 0, q_cnt = 0, ds_cnt = 0, free_cnt = 0;
+    uint32_t r_cnt = 0, q_cnt = 0, ds_cnt = 0, free_cnt = 0, s_issued = 0;
     bool ok = true;
     bool first_tile = true;
     const uint32_t led = lane == 0;  // the whole warp runs the issue code, this lane issues
-    const uint64_t dq_desc = desc_k_major(smem_u32(sQ)), ddo_desc = desc_k_major(smem_u32(sdO));
     const uint64_t ring_k = desc_k_major(smem_u32(sRing)), ring_mn = desc_mn_major(smem_u32(sRing));
     PT_DECL
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
       const int n = iterations(row_count(w));
       if (n == 0) continue;
       PT_MARK(0)
-      ok = mbar_wait(BAR(kQFull), q_cnt & 1, wctx, 410);
+      ok = mbar_wait(BAR(kQTmem), q_cnt & 1, wctx, 410);  // Q and dO of this tile sit in tensor memory
       if (!ok) break;
       PT_MARK(1)
       ++q_cnt;
       tc_fence_after();
-      const uint32_t base = r_cnt;  // ring position of K_0 of this tile; K_j at base+2j, V_j at base+2j+1
+      // the two landing stages go back to the ring
+      if (lane == 0) {
+        mbar_arrive(BAR(kREmpty + r_cnt % NS));
+        mbar_arrive(BAR(kREmpty + (r_cnt + 1) % NS));
+      }
+      __syncwarp();
+      const uint32_t base = r_cnt + 2;  // ring position of K_0 of this tile; K_j at base+2j, V_j at base+2j+1
       auto stage_of = [&](uint32_t pos) { return pos % NS; };
       auto wait_full = [&](uint32_t pos) {
         PT_MARK(0)
@@ -361,31 +381,34 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       };
       auto issue_s = [&](int j) -> bool {
         if (!wait_full(base + 2 * j)) return false;
-        tc_fence_after();
-        {
-          mma_ss_kk(tS[j & 1], dq_desc, ring_k + stage_of(base + 2 * j) * kTileDescStep, false, led);
-          umma_commit_led(BAR(kSFull + (j & 1)), led);
+        if (s_issued > 0) {  // the previous S has been loaded into registers by every compute thread
+          PT_MARK(0)
+          if (!mbar_wait(BAR(kSFree), (s_issued - 1) & 1, wctx, 414)) return false;
+          PT_MARK(5)
         }
-        __syncwarp();
+        ++s_issued;
+        tc_fence_after();
+        mma_ts_kk(tS, tQ, ring_k + stage_of(base + 2 * j) * kTileDescStep, false, led);
+        umma_commit_led(BAR(kSFull), led);
         return true;
       };
       auto issue_dp = [&](int j) -> bool {
         if (!wait_full(base + 2 * j + 1)) return false;
         tc_fence_after();
-        {
-          mma_ss_kk(tdP, ddo_desc, ring_k + stage_of(base + 2 * j + 1) * kTileDescStep, false, led);
-          umma_commit_led(BAR(kDpFull), led);
-          umma_commit_led(BAR(kREmpty + stage_of(base + 2 * j + 1)), led);  // V_j is only read by this MMA
-        }
-        __syncwarp();
+        mma_ts_kk(tdP, tdO, ring_k + stage_of(base + 2 * j + 1) * kTileDescStep, false, led);
+        umma_commit_led(BAR(kDpFull), led);
+        umma_commit_led(BAR(kREmpty + stage_of(base + 2 * j + 1)), led);  // V_j is only read by this MMA
         return true;
       };
       ok = issue_s(0);
       if (ok) ok = issue_dp(0);
-      if (ok && n > 1) ok = issue_s(1);
       for (int j = 0; j < n && ok; ++j) {
+        if (j + 1 < n) {
+          ok = issue_s(j + 1);  // runs under the exponentials of iteration j
+          if (!ok) break;
+        }
         PT_MARK(0)
-        ok = mbar_wait(BAR(kDsFull), ds_cnt & 1, wctx, 412);  // dS_j staged, dP and S_j consumed
+        ok = mbar_wait(BAR(kDsFull), ds_cnt & 1, wctx, 412);  // dS_j in tensor memory, dP_j consumed
         if (!ok) break;
         PT_MARK(3)
         ++ds_cnt;
@@ -404,20 +427,14 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           mma_ts_kmn(tdQ, tdP, tdP + 64u, ring_mn + sk * kTileDescStep, j > 0, led);
           umma_commit_led(BAR(kREmpty + sk), led);
         }
-        __syncwarp();
         if (j + 1 < n) {
           ok = issue_dp(j + 1);  // overwrites dS_j: in program order after the dQ MMAs that read it
           if (!ok) break;
         }
-        if (j + 2 < n) ok = issue_s(j + 2);
       }
       if (!ok) break;
-      {
-        umma_commit_led(BAR(kDqFinal), led);
-        umma_commit_led(BAR(kQEmpty), led);
-      }
-      __syncwarp();
-      r_cnt += 2 * n;
+      umma_commit_led(BAR(kDqFinal), led);
+      r_cnt += 2 + 2 * n;
       first_tile = false;
     }
     PT_MARK(0)
@@ -427,7 +444,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const int row = threadIdx.x & 127;
     const bool row_active = (BLK == 128) || (row < 64);  // warp-uniform
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    uint32_t r_cnt = 0, s_cnt[2] = {0, 0}, dp_cnt = 0, fin_cnt = 0;
+    uint32_t r_cnt = 0, s_cnt = 0, dp_cnt = 0, fin_cnt = 0;
     bool ok = true;
     PT_DECL
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
@@ -449,7 +466,37 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const float lse2 = row_active ? p.lse_log2[srow] : INFINITY;
       const float dlt = row_active ? p.delta[srow] : 0.f;
       const int32_t* idx_row = p.q2k_index + (long long)w * p.cap;
-      const uint32_t base = r_cnt;
+      // ---- move this tile's Q (group 0) or dO (group 1) from its ring stage into tensor memory: thread = row;
+      // the row's sixteen 16-byte chunks are read through the 128-byte swizzle and become 64 columns of packed
+      // bf16 pairs.  All MMAs of the previous tile have completed (its epilogue waited for them).
+      PT_MARK(0)
+      {
+        const uint32_t pos = r_cnt + (uint32_t)grp;  // Q at the tile's first ring position, dO at the second
+        r_cnt += 2 + 2 * (uint32_t)n;
+        ok = mbar_wait(BAR(kRFull + pos % NS), (pos / NS) & 1, wctx, 423);
+        if (!ok) break;
+        if (row_active) {
+          const uint8_t* tile = sRing + (pos % NS) * kTile;
+          const uint32_t dst = (grp ? tdO : tQ) + lane_base;
+#pragma unroll
+          for (int sl = 0; sl < 2; ++sl) {
+            uint32_t v[32];
+#pragma unroll
+            for (int ch = 0; ch < 8; ++ch) {
+              const uint4 x = *reinterpret_cast<const uint4*>(tile + sl * kSlab + row * 128 + ((ch ^ (row & 7)) << 4));
+              v[ch * 4 + 0] = x.x;
+              v[ch * 4 + 1] = x.y;
+              v[ch * 4 + 2] = x.z;
+              v[ch * 4 + 3] = x.w;
+            }
+            tmem_st32(dst + sl * 32, v);
+          }
+          tmem_wait_st();
+        }
+        tc_fence_before();
+        mbar_arrive(BAR(kQTmem));
+      }
+      PT_MARK(5)
       for (int j = 0; j < n && ok; ++j) {
         // valid kv tokens among this group's 64 columns of the 128-token tile
         int len;
@@ -460,12 +507,13 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
         // ---- phase 1: P = exp2(S*scale - lse)
         PT_MARK(0)
-        ok = mbar_wait(BAR(kSFull + (j & 1)), s_cnt[j & 1] & 1, wctx, 420);
+        ok = mbar_wait(BAR(kSFull), s_cnt & 1, wctx, 420);
         if (!ok) break;
         PT_MARK(1)
-        ++s_cnt[j & 1];
+        ++s_cnt;
         tc_fence_after();
         if (!row_active) {  // idle half of a 64-row tile: barrier protocol only
+          mbar_arrive(BAR(kSFree));
           ok = mbar_wait(BAR(kDpFull), dp_cnt & 1, wctx, 421);
           if (!ok) break;
           ++dp_cnt;
@@ -476,10 +524,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         float pr[64];
         {
           uint32_t* u = reinterpret_cast<uint32_t*>(pr);
-          tmem_ld32(tS[j & 1] + lane_base + grp * 64, u);
-          tmem_ld32(tS[j & 1] + lane_base + grp * 64 + 32, u + 32);
+          tmem_ld32(tS + lane_base + grp * 64, u);
+          tmem_ld32(tS + lane_base + grp * 64 + 32, u + 32);
           tmem_wait_ld();
         }
+        tc_fence_before();
+        mbar_arrive(BAR(kSFree));  // S_j is in registers: the next S may be computed
         const float neg_l = -lse2;
 #pragma unroll
         for (int c = 0; c < 64; c += 2)
@@ -515,7 +565,6 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         PT_MARK(4)
       }
       if (!ok) break;
-      r_cnt += 2 * n;
       // ---- epilogue: dQ * softmax_scale -> bf16 -> global
       ok = mbar_wait(BAR(kDqFinal), fin_cnt & 1, wctx, 422);
       if (!ok) break;
