@@ -83,6 +83,8 @@ class BwdArgs(ctypes.Structure):
         ("csr_offsets", ctypes.c_void_p),
         ("csr_indices", ctypes.c_void_p),
         ("block_sizes", ctypes.c_void_p),
+        ("work_order_q", ctypes.c_void_p),
+        ("work_order_kv", ctypes.c_void_p),
         ("workspace", ctypes.c_void_p),
         ("status", ctypes.c_void_p),
         ("workspace_bytes", ctypes.c_int64),

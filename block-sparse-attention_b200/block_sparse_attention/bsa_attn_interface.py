@@ -165,6 +165,19 @@ def _block_size_strides(block_sizes, batch, heads, num_kv_blocks, allow_ranks):
     return heads * num_kv_blocks, num_kv_blocks
 
 
+def _lpt_order(lib, counts: torch.Tensor, cap: int) -> torch.Tensor:
+    """Longest-first order of the rows of an int32 count tensor (stable; counts clamped to [0, cap])."""
+    device = counts.device
+    rows = counts.numel()
+    cap_sort = max(1, min(int(cap), 32000))
+    order = torch.empty(rows, dtype=torch.int32, device=device)
+    scratch = torch.empty(max(1, int(lib.bsa_lpt_order_scratch_ints(rows, cap_sort))), dtype=torch.int32, device=device)
+    with torch.cuda.device(device):
+        _cabi.check(lib.bsa_lpt_order(counts.data_ptr(), rows, cap_sort, order.data_ptr(), scratch.data_ptr(),
+                                      _cabi.stream_ptr(device)), "bsa_lpt_order")
+    return order
+
+
 def _launch_fwd(*, q, k, v, out, lse, q2k_block_index, q2k_block_nums, block_sizes, bs_strides, blk,
                 block_sparse_num, pack_gqa, splits, softmax_scale, dtype_code, q_scale=None, k_scale=None,
                 v_scale=None):
@@ -209,14 +222,7 @@ def _launch_fwd(*, q, k, v, out, lse, q2k_block_index, q2k_block_nums, block_siz
     work_order = None
     if q2k_block_nums is not None and q2k_block_nums.numel() > 2 * lib.bsa_num_sms(device.index or 0):
         # variable counts: longest-first work order so that the persistent CTAs finish together
-        rows = q2k_block_nums.numel()
-        cap_sort = min(int(args.cap), 32000)
-        work_order = torch.empty(rows, dtype=torch.int32, device=device)
-        scratch = torch.empty(max(1, int(lib.bsa_lpt_order_scratch_ints(rows, cap_sort))), dtype=torch.int32,
-                              device=device)
-        with torch.cuda.device(device):
-            _cabi.check(lib.bsa_lpt_order(q2k_block_nums.data_ptr(), rows, cap_sort, work_order.data_ptr(),
-                                          scratch.data_ptr(), _cabi.stream_ptr(device)), "bsa_lpt_order")
+        work_order = _lpt_order(lib, q2k_block_nums, int(args.cap))
         args.work_order = work_order.data_ptr()
     partial_o = partial_lse = None
     if splits > 1:
@@ -689,6 +695,14 @@ def bsa_attn_bwd(
     a.csr_offsets, a.csr_indices = offsets.data_ptr(), indices.data_ptr()
     a.block_sizes = _cabi.ptr(block_sizes)
     a.bs_stride_b, a.bs_stride_h = bs_strides
+    order_q = order_kv = None
+    if q2k_block_nums is not None and q2k_block_nums.numel() > 2 * lib.bsa_num_sms(device.index or 0):
+        # variable counts: both kernels walk their work items longest first, so the persistent CTAs finish
+        # together (query tiles by their count, KV blocks by the number of query tiles that attend them)
+        order_q = _lpt_order(lib, q2k_block_nums, q2k_block_index.shape[-1])
+        per_block = (offsets[..., 1:] - offsets[..., :-1]).sum(dim=2, dtype=torch.int32).contiguous()
+        order_kv = _lpt_order(lib, per_block, Nq)
+    a.work_order_q, a.work_order_kv = _cabi.ptr(order_q), _cabi.ptr(order_kv)
     a.workspace, a.workspace_bytes = workspace.data_ptr(), workspace.numel()
     a.status = _cabi.status_buffer(device).data_ptr()
     a.do_stride, a.q_stride = _cabi.strides3(views["dout"]), _cabi.strides3(views["q"])

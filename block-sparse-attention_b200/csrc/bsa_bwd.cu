@@ -37,6 +37,22 @@ constexpr int kBwdMmaWarp = 8;
 constexpr int kBwdLoadWarp = 9;
 constexpr int kDkvThreads = 352;  // dK/dV kernel: warps 8 and 9 issue MMAs, warp 10 loads
 constexpr int kDkvLoadWarp = 10;
+// Work item of this CTA in band `band`.  Natural order: CTA c takes c, G + c, 2G + c, ...  With a (longest-first)
+// order list the bands are walked back and forth (c, 2G-1-c, 2G+c, ...), so that every CTA gets a similar total.
+// Returns -1 when the band holds no item for this CTA.
+__device__ __forceinline__ int bwd_work_at(const int32_t* order, int band, int num_work, int* status) {
+  const int G = (int)gridDim.x, c = (int)blockIdx.x;
+  const int wi = band * G + ((order != nullptr && (band & 1)) ? (G - 1 - c) : c);
+  if (wi >= num_work) return -1;
+  if (order == nullptr) return wi;
+  int w = order[wi];
+  if (w < 0 || w >= num_work) {  // a corrupt order must not turn into a wild access
+    if (atomicCAS(status, 0, (int)kStatusBadIndex) == 0) status[2] = w;
+    w = 0;
+  }
+  return w;
+}
+
 constexpr int kTile = 128 * 128 * 2;  // bytes of one bf16 128x128 tile
 constexpr int kSlab = 128 * 128;      // bytes of one 64-column slab
 
@@ -45,6 +61,8 @@ struct BwdParams {
   const int32_t* __restrict__ q2k_nums;
   const int32_t* __restrict__ csr_offsets;
   const int32_t* __restrict__ csr_indices;
+  const int32_t* __restrict__ order_q;      // optional work orders (longest first) of the two main kernels
+  const int32_t* __restrict__ order_kv;
   const int32_t* __restrict__ block_sizes;  // optional valid-token counts of the KV blocks
   long long bs_stride_b, bs_stride_h;
   const float* __restrict__ lse_log2;  // [B,H,Nq*128]
@@ -309,7 +327,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   if (warp == kBwdLoadWarp) {
     uint32_t r_cnt = 0;
     bool ok = true;
-    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+    for (int band = 0; band * (int)gridDim.x < num_work && ok; ++band) {
+      const int w = bwd_work_at(p.order_q, band, num_work, p.status);
+      if (w < 0) continue;
       const int cnt = row_count(w);
       const int n = iterations(cnt);
       if (n == 0) continue;
@@ -356,7 +376,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     const uint32_t led = lane == 0;  // the whole warp runs the issue code, this lane issues
     const uint64_t ring_k = desc_k_major(smem_u32(sRing)), ring_mn = desc_mn_major(smem_u32(sRing));
     PT_DECL
-    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+    for (int band = 0; band * (int)gridDim.x < num_work && ok; ++band) {
+      const int w = bwd_work_at(p.order_q, band, num_work, p.status);
+      if (w < 0) continue;
       const int n = iterations(row_count(w));
       if (n == 0) continue;
       PT_MARK(0)
@@ -447,7 +469,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     uint32_t r_cnt = 0, s_cnt = 0, dp_cnt = 0, fin_cnt = 0;
     bool ok = true;
     PT_DECL
-    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+    for (int band = 0; band * (int)gridDim.x < num_work && ok; ++band) {
+      const int w = bwd_work_at(p.order_q, band, num_work, p.status);
+      if (w < 0) continue;
       const int cnt = row_count(w);
       const int n = iterations(cnt);
       const int m = w % p.Nq;
@@ -672,7 +696,9 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   if (warp == kDkvLoadWarp) {
     uint32_t r_cnt = 0, kv_cnt = 0, tile_cnt = 0;
     bool ok = true;
-    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+    for (int band = 0; band * (int)gridDim.x < num_work && ok; ++band) {
+      const int w = bwd_work_at(p.order_kv, band, num_work, p.status);
+      if (w < 0) continue;
       const int nb = w % p.Nkv;
       const int bh = w / p.Nkv;
       const int h = bh % p.H, b = bh / p.H;
@@ -752,7 +778,9 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint64_t k_desc = desc_k_major(smem_u32(sK)), v_desc = desc_k_major(smem_u32(sV));
     const uint64_t ring_k = desc_k_major(smem_u32(sRing)), ring_mn = desc_mn_major(smem_u32(sRing));
     PT_DECL
-    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+    for (int band = 0; band * (int)gridDim.x < num_work && ok; ++band) {
+      const int w = bwd_work_at(p.order_kv, band, num_work, p.status);
+      if (w < 0) continue;
       const int nb = w % p.Nkv;
       const int bh = w / p.Nkv;
       const int T = iterations(total_rows(bh, nb));
@@ -861,7 +889,9 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     uint32_t s_cnt = 0, dp_cnt = 0, fin_cnt = 0, tile_cnt = 0, r_cnt = 0;
     bool ok = true;
     PT_DECL
-    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+    for (int band = 0; band * (int)gridDim.x < num_work && ok; ++band) {
+      const int w = bwd_work_at(p.order_kv, band, num_work, p.status);
+      if (w < 0) continue;
       const int nb = w % p.Nkv;
       const int bh = w / p.Nkv;
       const int h = bh % p.H, b = bh / p.H;
@@ -1083,6 +1113,8 @@ extern "C" int bsa_bwd(const bsa_bwd_args* a, void* cuda_stream) {
   p.q2k_nums = a->q2k_nums;
   p.csr_offsets = a->csr_offsets;
   p.csr_indices = a->csr_indices;
+  p.order_q = a->work_order_q;
+  p.order_kv = a->work_order_kv;
   p.block_sizes = a->block_sizes;
   p.bs_stride_b = a->bs_stride_b;
   p.bs_stride_h = a->bs_stride_h;

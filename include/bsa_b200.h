@@ -222,6 +222,9 @@ int bsa_build_k2q_csr(const int32_t* q2k_index, const int32_t* q2k_nums, int32_t
  * csrc/bwd/sm100_blk128/bsa_bwd_sm100.py:2178-2385 (blk128) and of the blk64 driver
  * bsa_attn_interface.py:4022-4290 over csrc/bwd/sm100_blk64/bsa_bwd_sm100.py (preprocess
  * csrc/bwd/bsa_bwd_preprocess.py, postprocess csrc/bwd/bsa_bwd_postprocess.py).
+ *   work_order_q / work_order_kv: NULL (natural order), or the order in which the persistent CTAs of the two
+ *   main kernels walk their work items (CTA c takes entries c, 2G-1-c, 2G+c, ... of it, G = grid size); a
+ *   longest-first order from bsa_lpt_order balances skewed per-row counts, as in the forward;
  *   block_sizes: NULL, or int32 valid-token counts of the KV blocks with element strides
  *   (bs_stride_b, bs_stride_h, 1); tokens beyond a block's count get no probability and zero dK / dV,
  *   exactly as the forward masks them (the reference's blk128 backward ignores block_sizes, its blk64
@@ -245,6 +248,8 @@ typedef struct bsa_bwd_args {
   const int32_t* csr_offsets;
   const int32_t* csr_indices;
   const int32_t* block_sizes;
+  const int32_t* work_order_q;  /* NULL, or a permutation of the B*H*Nq query tiles (dQ kernel) */
+  const int32_t* work_order_kv; /* NULL, or a permutation of the B*H*Nkv KV blocks (dK/dV kernel) */
   void* workspace;
   int32_t* status;
   int64_t workspace_bytes;

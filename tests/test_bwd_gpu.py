@@ -224,6 +224,26 @@ def test_head_dimension_64_with_128_token_blocks():
                      sparse_block_size=64)
 
 
+@pytest.mark.parametrize("blk", [128, 64])
+def test_skewed_counts_walk_longest_first(blk):
+    """more than two work items per SM with per-row counts: both kernels take the longest-first order
+    (query tiles by count, KV blocks by the number of tiles attending them); results must not depend on it."""
+    S = 8192 if blk == 128 else 4096
+    counts = [1, 2, 1, 64 if blk == 128 else 64, 3, 1, 2, 1, 1, 5]
+    q, k, v, do, index, nums = _case(21, 2, 4, S, S, counts, blk=blk)
+    assert nums.numel() > 2 * 148
+    got = _run(q, k, v, do, index, 0, nums=nums, blk=blk)
+    Nkv = S // blk
+    gq, gk, gv = orc.backward_gathered(q, k, v, do, index.clamp(max=Nkv - 1), 0, nums=nums, blk=blk, heads=[3],
+                                       batches=[1])
+    for g, ref in zip(got, (gq, gk, gv)):
+        assert torch.isfinite(g).all()
+        assert (g[1, 3] - ref[1, 3]).abs().max().item() < 6e-2
+    again = _run(q, k, v, do, index, 0, nums=nums, blk=blk)
+    for x, y in zip(got, again):
+        assert torch.equal(x, y)
+
+
 def test_argument_errors():
     from block_sparse_attention import bsa_attn_bwd
     x = torch.zeros(1, 2, 128, 128, device="cuda").bfloat16()
