@@ -371,8 +371,10 @@ def main():
         d2h = sum(t.numel() * t.element_size() for t in host_out.values()) + host_lse.numel() * 4
 
         from block_sparse_attention.host_pipeline import HostPipeline
-        # the public host-memory entry: head chunks pipelined over copy / compute / copy streams
-        pipe = HostPipeline(Bp, H, S, S, idx, count, heads_per_chunk=8)
+        # the public host-memory entry: head chunks pipelined over copy / compute / copy streams.  Two heads per
+        # chunk: the first copy in and the last copy out are the only ones nothing overlaps, so short chunks win
+        # until the per-chunk launches dominate (8 / 4 / 2 / 1 heads: 52.8 / 51.0 / 48.4 / 51.1 ms on this shape)
+        pipe = HostPipeline(Bp, H, S, S, idx, count, heads_per_chunk=2)
         host_res = {"out": host_out["o"], "lse": host_lse, "dq": host_out["dq"], "dk": host_out["dk"],
                     "dv": host_out["dv"]}
         host_src = {"q": host["q"], "k": host["k"], "v": host["v"], "dout": host["do"]}
