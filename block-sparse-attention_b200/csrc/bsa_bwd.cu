@@ -18,7 +18,7 @@
 // :1864, :2351), its preprocess csrc/bwd/bsa_bwd_preprocess.py:184-324 and its CSR walk :86-112.
 //
 // Warp roles (both kernels): warps 0-7 compute (two groups of 128 threads, thread = tensor-memory lane,
-// group g owns columns [64g, 64g+64) of the score tiles), warp 8 MMA issue, warp 9 TMA producer.
+// group g owns columns [64g, 64g+64) of the score tiles), warps 8-9 MMA issue, warp 10 TMA producer.
 #include "../../include/bsa_b200.h"
 #include "bsa_common.cuh"
 #include "bsa_host.h"
@@ -32,9 +32,9 @@ __device__ unsigned long long g_bwd_prof[128];
 
 namespace bsa {
 
-constexpr int kBwdThreads = 320;
 constexpr int kBwdMmaWarp = 8;
-constexpr int kBwdLoadWarp = 9;
+constexpr int kDqThreads = 384;  // dQ kernel: warps 8, 9 and 10 issue MMAs, warp 11 loads
+constexpr int kDqLoadWarp = 11;
 constexpr int kDkvThreads = 352;  // dK/dV kernel: warps 8 and 9 issue MMAs, warp 10 loads
 constexpr int kDkvLoadWarp = 10;
 // Work item of this CTA in band `band`.  Natural order: CTA c takes c, G + c, 2G + c, ...  With a (longest-first)
@@ -243,35 +243,29 @@ __device__ __forceinline__ void mma_ts_kmn(uint32_t d, uint32_t a_lo, uint32_t a
 // ------------------------------------------------------------------------------------------------
 // 2. dQ kernel
 // ------------------------------------------------------------------------------------------------
-// smem: one ring of 7 tiles | barriers | misc.  Per query tile the ring carries Q, dO, K_0, V_0, K_1, V_1, ...
-// Q and dO only land there: the compute warps move them into tensor memory once per tile (thread = row), so the
-// S and dP MMAs read their stationary operand from tensor memory, the two stages go straight back to the ring,
-// and K / V tiles are prefetched three to four stages ahead.
-// Tensor memory: S @0, dP @128 (dS overwrites the head of each group's half), dQ @256, Q @384, dO @448.
-// S is single-buffered: S_{j+1} is issued as soon as every compute thread has loaded S_j into registers, i.e.
-// it runs under the exponentials of iteration j.
-constexpr int kDqStages = 7;
-constexpr int kDqSmem = kDqStages * kTile + BwdSmem::kBarBytes + BwdSmem::kMisc;
-
-// D = A(tmem bf16, 64 columns: rows = lanes, contraction packed two per column) * B(smem, K-major)^T
-__device__ __forceinline__ void mma_ts_kk(uint32_t d, uint32_t a_tmem, uint64_t b_desc, bool acc, uint32_t led) {
-#pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    const uint64_t off = (uint64_t)((k >> 2) * (kSlab >> 4) + (k & 3) * 2);
-    umma_f16_ts_led(d, a_tmem + (uint32_t)k * 8u, b_desc + off, kIdescKK, (acc || k > 0) ? 1u : 0u, led);
-  }
-}
+// smem: Q | dO | ring of 5 tiles (K_0, V_0, K_1, V_1, ...) | barriers | misc.  Q and dO stay in their buffers for
+// the whole tile (the S and dP MMAs read them from shared memory) and are released after the tile's last S / dP
+// MMA, about one iteration before the tile ends, so the next tile's Q and dO arrive under the last iteration.
+// Tensor memory: S @0, dP / dS buffer 0 @128, buffer 1 @256 (dS overwrites the head of each group's half), dQ @384.
+// Nothing an MMA produces for iteration j+1 depends on what the compute threads produce in iteration j:
+// S is single-buffered but S_{j+1} is issued as soon as every compute thread has loaded S_j into registers, and
+// dP_{j+1} goes to the buffer that dQ_{j-1} has finished reading, so both run under the arithmetic of iteration j
+// and the compute threads wait for neither in steady state.
+constexpr int kDqStages = 5;  // K / V ring; Q and dO have a buffer each in front of it
+constexpr int kDqSmem = (2 + kDqStages) * kTile + BwdSmem::kBarBytes + BwdSmem::kMisc;
 
 // BLK = 64: the query tile has 64 rows (top half of the 128-row MMAs, lanes 64-127 idle) and one KV iteration
 // gathers two 64-token blocks into a 128-token tile (an odd count re-loads the last block as a masked phantom);
 // compute group g then owns exactly block g of the pair.
 template <int BLK>
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(kDqThreads, 1)
 bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
               const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v, const BwdParams p) {
   constexpr int NS = kDqStages;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* sRing = smem_raw;
+  uint8_t* sQ = smem_raw;
+  uint8_t* sdO = sQ + kTile;
+  uint8_t* sRing = sdO + kTile;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sRing + NS * kTile);
   uint32_t& s_tmem_base = *reinterpret_cast<uint32_t*>(bars + 32);
   volatile int& s_abort = *reinterpret_cast<volatile int*>(bars + 33);
@@ -281,10 +275,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   }
   const uint32_t bar_base = smem_u32(bars);
   auto BAR = [&](int i) { return bar_base + (uint32_t)i * 8u; };
-  // ring_full[NS], ring_empty[NS], s_full, s_free, dp_full, ds_full, dq_final, dq_free, q_tmem
-  constexpr int kRFull = 0, kREmpty = NS, kSFull = 2 * NS, kSFree = kSFull + 1, kDpFull = kSFree + 1,
-                kDsFull = kDpFull + 1, kDqFinal = kDsFull + 1, kDqFree = kDqFinal + 1, kQTmem = kDqFree + 1,
-                kNumBars = kQTmem + 1;
+  // ring_full[NS], ring_empty[NS], q_full, q_empty, do_full, do_empty, s_full, s_free, dp_full[2], ds_full[2],
+  // ds_used[2], dq_final, dq_free
+  constexpr int kRFull = 0, kREmpty = NS, kQFull = 2 * NS, kQEmpty = kQFull + 1, kDoFull = kQEmpty + 1,
+                kDoEmpty = kDoFull + 1, kSFull = kDoEmpty + 1, kSFree = kSFull + 1, kDpFull = kSFree + 1,
+                kDsFull = kDpFull + 2, kDsUsed = kDsFull + 2, kDqFinal = kDsUsed + 2, kDqFree = kDqFinal + 1,
+                kNumBars = kDqFree + 1;
   static_assert(kNumBars <= 32, "barrier slots");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   WaitCtx wctx{&s_abort, p.status};
@@ -292,13 +288,19 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     s_abort = 0;
     for (int i = 0; i < NS; ++i) {
       mbar_init(BAR(kRFull + i), 1);
-      mbar_init(BAR(kREmpty + i), 1);
+      mbar_init(BAR(kREmpty + i), 3);  // released once by each issuing warp
     }
+    mbar_init(BAR(kQFull), 1);
+    mbar_init(BAR(kQEmpty), 1);
+    mbar_init(BAR(kDoFull), 1);
+    mbar_init(BAR(kDoEmpty), 1);
     mbar_init(BAR(kSFull), 1);
     mbar_init(BAR(kSFree), 256);   // every compute thread has loaded its part of S_j: S_{j+1} may overwrite it
-    mbar_init(BAR(kQTmem), 256);   // Q and dO of the tile are in tensor memory
-    mbar_init(BAR(kDpFull), 1);
-    mbar_init(BAR(kDsFull), 256);
+    for (int i = 0; i < 2; ++i) {  // the two dP / dS buffers, by iteration parity
+      mbar_init(BAR(kDpFull + i), 1);
+      mbar_init(BAR(kDsFull + i), 256);
+      mbar_init(BAR(kDsUsed + i), 1);  // the dQ MMAs have read dS from the buffer: it may take the dP after next
+    }
     mbar_init(BAR(kDqFinal), 1);
     mbar_init(BAR(kDqFree), 256);
     mbar_fence_init();
@@ -312,7 +314,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = s_tmem_base;
-  const uint32_t tS = tmem, tdP = tmem + 128u, tdQ = tmem + 256u, tQ = tmem + 384u, tdO = tmem + 448u;
+  const uint32_t tS = tmem, tdP = tmem + 128u, tdQ = tmem + 384u;  // dP / dS buffer i at tdP + 128 i
   const int num_work = p.B * p.H * p.Nq;
 
   constexpr int kPerIt = 128 / BLK;               // KV blocks per 128-token iteration
@@ -322,10 +324,10 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     return max(0, min(c, p.cap));
   };
   auto iterations = [&](int count) { return (count + kPerIt - 1) / kPerIt; };
-  // ring positions of a tile with n iterations: Q, dO, then K_j at +2+2j and V_j at +3+2j
+  // ring positions of a tile with n iterations: K_j at +2j and V_j at +2j+1
 
-  if (warp == kBwdLoadWarp) {
-    uint32_t r_cnt = 0;
+  if (warp == kDqLoadWarp) {
+    uint32_t r_cnt = 0, tile_cnt = 0;
     bool ok = true;
     for (int band = 0; band * (int)gridDim.x < num_work && ok; ++band) {
       const int w = bwd_work_at(p.order_q, band, num_work, p.status);
@@ -338,17 +340,17 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const int b = w / (p.Nq * p.H);
       const int32_t* row = p.q2k_index + (long long)w * p.cap;
       for (int which = 0; which < 2 && ok; ++which) {  // Q, dO
-        const uint32_t stage = r_cnt % NS, ph = (r_cnt / NS) & 1;
-        ok = mbar_wait(BAR(kREmpty + stage), ph ^ 1, wctx, 400);
+        const int full = which ? kDoFull : kQFull, empty = which ? kDoEmpty : kQEmpty;
+        ok = mbar_wait(BAR(empty), (tile_cnt & 1) ^ 1, wctx, 400);
         if (!ok) break;
         if (lane == 0) {
-          mbar_arrive_expect_tx(BAR(kRFull + stage), kQBytes);
+          mbar_arrive_expect_tx(BAR(full), kQBytes);
           const CUtensorMap* tm = which ? &tm_do : &tm_q;
           for (int sl = 0; sl < 2; ++sl)
-            tma_load_4d(smem_u32(sRing + stage * kTile + sl * kSlab), tm, BAR(kRFull + stage), sl * 64, m * BLK, h, b);
+            tma_load_4d(smem_u32((which ? sdO : sQ) + sl * kSlab), tm, BAR(full), sl * 64, m * BLK, h, b);
         }
-        ++r_cnt;
       }
+      ++tile_cnt;
       for (int j = 0; j < n && ok; ++j) {
         const int blk0 = row[kPerIt * j];
         const int blk1 = (BLK == 64 && 2 * j + 1 < cnt) ? row[2 * j + 1] : blk0;
@@ -369,8 +371,17 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
       }
     }
-  } else if (warp == kBwdMmaWarp) {
-    uint32_t r_cnt = 0, q_cnt = 0, ds_cnt = 0, free_cnt = 0, s_issued = 0;
+  } else if (warp >= kBwdMmaWarp && warp < kBwdMmaWarp + 3) {
+    // Three issuing warps, one per dependency chain (a thread that issues MMAs is stalled at their execution rate,
+    // so one thread issuing S and dP in turn delivers S late):
+    //   issuer 0: S_j = Q K_j^T; S_{j+1} once every compute thread holds S_j in registers.
+    //   issuer 1: dQ += dS_j K_j.
+    //   issuer 2: dP_j = dO V_j^T; dP_{j+1} (buffer (j+1) & 1) once dQ_{j-1} has read dS_{j-1} from that buffer.
+    // Neither S nor dP waits for anything the compute threads produce in the running iteration.
+    // All three visit every ring position in increasing order and release every stage once (a commit after the last MMA
+    // that reads the tile, a plain arrival for a tile the issuer does not read).
+    const int who = warp - kBwdMmaWarp;
+    uint32_t r_cnt = 0, free_cnt = 0, s_issued = 0, dp_issued = 0, ds_seen = 0, tile_cnt = 0;
     bool ok = true;
     bool first_tile = true;
     const uint32_t led = lane == 0;  // the whole warp runs the issue code, this lane issues
@@ -381,19 +392,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       if (w < 0) continue;
       const int n = iterations(row_count(w));
       if (n == 0) continue;
-      PT_MARK(0)
-      ok = mbar_wait(BAR(kQTmem), q_cnt & 1, wctx, 410);  // Q and dO of this tile sit in tensor memory
-      if (!ok) break;
-      PT_MARK(1)
-      ++q_cnt;
-      tc_fence_after();
-      // the two landing stages go back to the ring
-      if (lane == 0) {
-        mbar_arrive(BAR(kREmpty + r_cnt % NS));
-        mbar_arrive(BAR(kREmpty + (r_cnt + 1) % NS));
-      }
-      __syncwarp();
-      const uint32_t base = r_cnt + 2;  // ring position of K_0 of this tile; K_j at base+2j, V_j at base+2j+1
+      const uint32_t base = r_cnt;  // K_j at base + 2j, V_j at base + 2j + 1
       auto stage_of = [&](uint32_t pos) { return pos % NS; };
       auto wait_full = [&](uint32_t pos) {
         PT_MARK(0)
@@ -401,72 +400,113 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         PT_MARK(2)
         return r;
       };
-      auto issue_s = [&](int j) -> bool {
-        if (!wait_full(base + 2 * j)) return false;
-        if (s_issued > 0) {  // the previous S has been loaded into registers by every compute thread
-          PT_MARK(0)
-          if (!mbar_wait(BAR(kSFree), (s_issued - 1) & 1, wctx, 414)) return false;
-          PT_MARK(5)
-        }
-        ++s_issued;
-        tc_fence_after();
-        mma_ts_kk(tS, tQ, ring_k + stage_of(base + 2 * j) * kTileDescStep, false, led);
-        umma_commit_led(BAR(kSFull), led);
+      auto pass = [&](uint32_t pos) {  // a tile this issuer does not read
+        if (!wait_full(pos)) return false;
+        if (led) mbar_arrive(BAR(kREmpty + stage_of(pos)));
+        __syncwarp();
         return true;
       };
-      auto issue_dp = [&](int j) -> bool {
-        if (!wait_full(base + 2 * j + 1)) return false;
-        tc_fence_after();
-        mma_ts_kk(tdP, tdO, ring_k + stage_of(base + 2 * j + 1) * kTileDescStep, false, led);
-        umma_commit_led(BAR(kDpFull), led);
-        umma_commit_led(BAR(kREmpty + stage_of(base + 2 * j + 1)), led);  // V_j is only read by this MMA
-        return true;
-      };
-      ok = issue_s(0);
-      if (ok) ok = issue_dp(0);
-      for (int j = 0; j < n && ok; ++j) {
-        if (j + 1 < n) {
-          ok = issue_s(j + 1);  // runs under the exponentials of iteration j
-          if (!ok) break;
-        }
+      if (who == 0) {
         PT_MARK(0)
-        ok = mbar_wait(BAR(kDsFull), ds_cnt & 1, wctx, 412);  // dS_j in tensor memory, dP_j consumed
+        ok = mbar_wait(BAR(kQFull), tile_cnt & 1, wctx, 410);
+        PT_MARK(1)
+        const uint64_t q_desc = desc_k_major(smem_u32(sQ));
+        for (int j = 0; j < n && ok; ++j) {
+          ok = wait_full(base + 2 * j);  // K_j
+          if (!ok) break;
+          if (s_issued > 0) {  // the previous S has been loaded into registers by every compute thread
+            PT_MARK(0)
+            ok = mbar_wait(BAR(kSFree), (s_issued - 1) & 1, wctx, 414);
+            if (!ok) break;
+            PT_MARK(5)
+          }
+          ++s_issued;
+          tc_fence_after();
+          {
+            const uint32_t sk = stage_of(base + 2 * j);
+            mma_ss_kk(tS, q_desc, ring_k + sk * kTileDescStep, false, led);
+            umma_commit_led(BAR(kSFull), led);
+            umma_commit_led(BAR(kREmpty + sk), led);
+            if (j == n - 1) umma_commit_led(BAR(kQEmpty), led);  // the tile's last S: Q may be replaced
+          }
+          __syncwarp();
+          ok = pass(base + 2 * j + 1);  // V_j
+        }
         if (!ok) break;
-        PT_MARK(3)
-        ++ds_cnt;
-        if (j == 0 && !first_tile) {  // the previous tile's epilogue has drained dQ
+      } else if (who == 2) {
+        PT_MARK(0)
+        ok = mbar_wait(BAR(kDoFull), tile_cnt & 1, wctx, 416);
+        PT_MARK(1)
+        const uint64_t do_desc = desc_k_major(smem_u32(sdO));
+        for (int j = 0; j < n && ok; ++j) {
+          ok = pass(base + 2 * j);  // K_j
+          if (ok) ok = wait_full(base + 2 * j + 1);  // V_j
+          if (!ok) break;
+          const uint32_t buf = dp_issued & 1;
+          if (dp_issued >= 2) {  // dS of two iterations back has been read from this buffer
+            PT_MARK(0)
+            ok = mbar_wait(BAR(kDsUsed + buf), ((dp_issued >> 1) - 1) & 1, wctx, 415);
+            if (!ok) break;
+            PT_MARK(3)
+          }
+          ++dp_issued;
+          tc_fence_after();
+          {
+            const uint32_t sv = stage_of(base + 2 * j + 1);
+            mma_ss_kk(tdP + buf * 128u, do_desc, ring_k + sv * kTileDescStep, false, led);
+            umma_commit_led(BAR(kDpFull + buf), led);
+            umma_commit_led(BAR(kREmpty + sv), led);
+            if (j == n - 1) umma_commit_led(BAR(kDoEmpty), led);  // the tile's last dP: dO may be replaced
+          }
+          __syncwarp();
+        }
+        if (!ok) break;
+      } else {
+        for (int j = 0; j < n && ok; ++j) {
+          ok = wait_full(base + 2 * j);  // K_j
+          if (ok) ok = pass(base + 2 * j + 1);  // V_j
+          if (!ok) break;
+          const uint32_t buf = ds_seen & 1;
           PT_MARK(0)
-          ok = mbar_wait(BAR(kDqFree), free_cnt & 1, wctx, 413);
+          ok = mbar_wait(BAR(kDsFull + buf), (ds_seen >> 1) & 1, wctx, 412);  // dS_j in tensor memory
           if (!ok) break;
-          PT_MARK(4)
-          ++free_cnt;
+          PT_MARK(3)
+          ++ds_seen;
+          if (j == 0 && !first_tile) {  // the previous tile's epilogue has drained dQ
+            PT_MARK(0)
+            ok = mbar_wait(BAR(kDqFree), free_cnt & 1, wctx, 413);
+            if (!ok) break;
+            PT_MARK(4)
+            ++free_cnt;
+          }
+          tc_fence_after();
+          {
+            const uint32_t sk = stage_of(base + 2 * j);
+            // dQ += dS_j (bf16 in tensor memory, at the head of each group's half of the buffer) * K_j
+            // (MN-major view of the K tile)
+            const uint32_t t = tdP + buf * 128u;
+            mma_ts_kmn(tdQ, t, t + 64u, ring_mn + sk * kTileDescStep, j > 0, led);
+            umma_commit_led(BAR(kDsUsed + buf), led);
+            umma_commit_led(BAR(kREmpty + sk), led);
+          }
+          __syncwarp();
         }
-        tc_fence_after();
-        {
-          const uint32_t sk = stage_of(base + 2 * j);
-          // dQ += dS_j (bf16 in tensor memory, at the head of each group's half of the dP columns) * K_j
-          // (MN-major view of the K tile)
-          mma_ts_kmn(tdQ, tdP, tdP + 64u, ring_mn + sk * kTileDescStep, j > 0, led);
-          umma_commit_led(BAR(kREmpty + sk), led);
-        }
-        if (j + 1 < n) {
-          ok = issue_dp(j + 1);  // overwrites dS_j: in program order after the dQ MMAs that read it
-          if (!ok) break;
-        }
+        if (!ok) break;
+        umma_commit_led(BAR(kDqFinal), led);
+        __syncwarp();
       }
-      if (!ok) break;
-      umma_commit_led(BAR(kDqFinal), led);
-      r_cnt += 2 + 2 * n;
+      r_cnt += 2 * n;
+      ++tile_cnt;
       first_tile = false;
     }
     PT_MARK(0)
-    PTB_FLUSH(16)
+    if (who == 0) { PTB_FLUSH(16) } else if (who == 1) { PTB_FLUSH(24) } else { PTB_FLUSH(32) }
   } else if (warp < 8) {
     const int grp = warp >> 2;
     const int row = threadIdx.x & 127;
     const bool row_active = (BLK == 128) || (row < 64);  // warp-uniform
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    uint32_t r_cnt = 0, s_cnt = 0, dp_cnt = 0, fin_cnt = 0;
+    uint32_t s_cnt = 0, dp_cnt = 0, fin_cnt = 0;
     bool ok = true;
     PT_DECL
     for (int band = 0; band * (int)gridDim.x < num_work && ok; ++band) {
@@ -490,37 +530,6 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const float lse2 = row_active ? p.lse_log2[srow] : INFINITY;
       const float dlt = row_active ? p.delta[srow] : 0.f;
       const int32_t* idx_row = p.q2k_index + (long long)w * p.cap;
-      // ---- move this tile's Q (group 0) or dO (group 1) from its ring stage into tensor memory: thread = row;
-      // the row's sixteen 16-byte chunks are read through the 128-byte swizzle and become 64 columns of packed
-      // bf16 pairs.  All MMAs of the previous tile have completed (its epilogue waited for them).
-      PT_MARK(0)
-      {
-        const uint32_t pos = r_cnt + (uint32_t)grp;  // Q at the tile's first ring position, dO at the second
-        r_cnt += 2 + 2 * (uint32_t)n;
-        ok = mbar_wait(BAR(kRFull + pos % NS), (pos / NS) & 1, wctx, 423);
-        if (!ok) break;
-        if (row_active) {
-          const uint8_t* tile = sRing + (pos % NS) * kTile;
-          const uint32_t dst = (grp ? tdO : tQ) + lane_base;
-#pragma unroll
-          for (int sl = 0; sl < 2; ++sl) {
-            uint32_t v[32];
-#pragma unroll
-            for (int ch = 0; ch < 8; ++ch) {
-              const uint4 x = *reinterpret_cast<const uint4*>(tile + sl * kSlab + row * 128 + ((ch ^ (row & 7)) << 4));
-              v[ch * 4 + 0] = x.x;
-              v[ch * 4 + 1] = x.y;
-              v[ch * 4 + 2] = x.z;
-              v[ch * 4 + 3] = x.w;
-            }
-            tmem_st32(dst + sl * 32, v);
-          }
-          tmem_wait_st();
-        }
-        tc_fence_before();
-        mbar_arrive(BAR(kQTmem));
-      }
-      PT_MARK(5)
       for (int j = 0; j < n && ok; ++j) {
         // valid kv tokens among this group's 64 columns of the 128-token tile
         int len;
@@ -536,13 +545,14 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         PT_MARK(1)
         ++s_cnt;
         tc_fence_after();
+        const uint32_t buf = dp_cnt & 1;  // dP / dS buffer of this iteration
         if (!row_active) {  // idle half of a 64-row tile: barrier protocol only
           mbar_arrive(BAR(kSFree));
-          ok = mbar_wait(BAR(kDpFull), dp_cnt & 1, wctx, 421);
+          ok = mbar_wait(BAR(kDpFull + buf), (dp_cnt >> 1) & 1, wctx, 421);
           if (!ok) break;
           ++dp_cnt;
           tc_fence_before();
-          mbar_arrive(BAR(kDsFull));
+          mbar_arrive(BAR(kDsFull + buf));
           continue;
         }
         float pr[64];
@@ -562,16 +572,17 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 #pragma unroll
           for (int c = 0; c < 64; ++c) pr[c] = (c < len) ? pr[c] : 0.f;
         }
-        // ---- phase 2: dS = P o (dP - delta) -> bf16 -> tensor memory (head of this group's half of dP)
+        // ---- phase 2: dS = P o (dP - delta) -> bf16 -> tensor memory (head of this group's half of the buffer)
         PT_MARK(2)
-        ok = mbar_wait(BAR(kDpFull), dp_cnt & 1, wctx, 421);
+        ok = mbar_wait(BAR(kDpFull + buf), (dp_cnt >> 1) & 1, wctx, 421);
         if (!ok) break;
         PT_MARK(3)
         ++dp_cnt;
         tc_fence_after();
+        const uint32_t tbuf = tdP + buf * 128u + lane_base + grp * 64;
         uint32_t dp[64];
-        tmem_ld32(tdP + lane_base + grp * 64, dp);
-        tmem_ld32(tdP + lane_base + grp * 64 + 32, dp + 32);
+        tmem_ld32(tbuf, dp);
+        tmem_ld32(tbuf + 32, dp + 32);
         tmem_wait_ld();
         {
           uint32_t pk[32];
@@ -581,11 +592,11 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             const float d1 = pr[2 * e + 1] * (__uint_as_float(dp[2 * e + 1]) - dlt);
             pk[e] = pack_bf16x2(d0, d1);
           }
-          tmem_st32(tdP + lane_base + grp * 64, pk);
+          tmem_st32(tbuf, pk);
           tmem_wait_st();
         }
         tc_fence_before();
-        mbar_arrive(BAR(kDsFull));
+        mbar_arrive(BAR(kDsFull + buf));
         PT_MARK(4)
       }
       if (!ok) break;
@@ -1153,7 +1164,7 @@ extern "C" int bsa_bwd(const bsa_bwd_args* a, void* cuda_stream) {
   if (work_q > 0x7fffffffLL || work_kv > 0x7fffffffLL) return set_error(BSA_ERR_UNSUPPORTED, "bsa_bwd: too many tiles");
   const int grid_q = (int)(work_q < num_sms ? work_q : num_sms);
   const int grid_kv = (int)(work_kv < num_sms ? work_kv : num_sms);
-  dq_kernel<<<grid_q, kBwdThreads, kDqSmem, st>>>(tq, tdo, tk, tv, p);
+  dq_kernel<<<grid_q, kDqThreads, kDqSmem, st>>>(tq, tdo, tk, tv, p);
   e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "bwd dQ launch: %s", cudaGetErrorString(e));
   dkv_kernel<<<grid_kv, kDkvThreads, kDkvSmem, st>>>(tq, tdo, tk, tv, p);
