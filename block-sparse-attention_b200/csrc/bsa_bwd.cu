@@ -4,8 +4,8 @@
 //   1. preprocess : delta[row] = sum_d O*dO, lse_log2[row] = lse*log2(e) (+inf for empty rows so that
 //                   the recomputed probabilities are exactly 0), both padded to whole 128-row tiles
 //   2. dQ kernel  : one work item per query tile, driven by the q2k index.  Per selected KV block:
-//                   S = Q K^T, dP = dO V^T, P = exp2(S*scale - lse), dS = P o (dP - delta) (bf16, staged
-//                   in shared memory), dQ += dS K.  dQ stays in tensor memory for the whole tile.
+//                   S = Q K^T, dP = dO V^T, P = exp2(S*scale - lse), dS = P o (dP - delta) (bf16, back to
+//                   tensor memory), dQ += dS K.  dQ stays in tensor memory for the whole tile.
 //   3. dK/dV kernel: one work item per KV block, driven by the k2q CSR (all query groups of the block
 //                   are walked by the same CTA, so nothing has to be reduced across CTAs).  Per query
 //                   tile of the CSR row: S^T = K Q^T, dP^T = V dO^T, P^T and dS^T (bf16) go back to
@@ -530,14 +530,15 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
       const float lse2 = row_active ? p.lse_log2[srow] : INFINITY;
       const float dlt = row_active ? p.delta[srow] : 0.f;
       const int32_t* idx_row = p.q2k_index + (long long)w * p.cap;
+      // valid kv tokens among this group's 64 columns of the 128-token tile of iteration j; fetched one iteration
+      // ahead so that the index load never sits in front of the arithmetic
+      auto valid_len = [&](int j) -> int {
+        if (BLK == 128) return bwd_block_len<128>(p, b, h, idx_row[j]) - grp * 64;
+        return (2 * j + grp < cnt) ? bwd_block_len<64>(p, b, h, idx_row[2 * j + grp]) : 0;
+      };
+      int len_next = valid_len(0);
       for (int j = 0; j < n && ok; ++j) {
-        // valid kv tokens among this group's 64 columns of the 128-token tile
-        int len;
-        if (BLK == 128) {
-          len = bwd_block_len<128>(p, b, h, idx_row[j]) - grp * 64;
-        } else {
-          len = (2 * j + grp < cnt) ? bwd_block_len<64>(p, b, h, idx_row[2 * j + grp]) : 0;
-        }
+        const int len = len_next;
         // ---- phase 1: P = exp2(S*scale - lse)
         PT_MARK(0)
         ok = mbar_wait(BAR(kSFull), s_cnt & 1, wctx, 420);
@@ -564,6 +565,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         }
         tc_fence_before();
         mbar_arrive(BAR(kSFree));  // S_j is in registers: the next S may be computed
+        if (j + 1 < n) len_next = valid_len(j + 1);
         const float neg_l = -lse2;
 #pragma unroll
         for (int c = 0; c < 64; c += 2)
@@ -629,9 +631,13 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 // ------------------------------------------------------------------------------------------------
 // 3. dK/dV kernel
 // ------------------------------------------------------------------------------------------------
-// smem: K | V | ring of 4 tiles (Q_i, dO_i alternating) | stats ring [4][2][128] f32 | barriers | misc
-constexpr int kDkvStages = 4;
-constexpr int kStatSlots = 4;
+// smem: K | V | ring of 5 tiles (Q_i, dO_i alternating) | row statistics [2][2][128] f32 | barriers | misc
+// Tensor memory: X @0 takes S^T_i and, once every compute thread holds S^T_i in registers, dP^T_i; once that is
+// in registers too, S^T_{i+1}.  Y @128 takes P^T_i and dS^T_i (bf16, 32 columns each per compute group), the
+// tensor-memory operands of dV @256 += P^T dO and dK @384 += dS^T Q.  No MMA result that iteration i+1 needs waits
+// for an MMA that consumes what the compute threads produce in iteration i.
+constexpr int kDkvStages = 5;
+constexpr int kStatSlots = 2;
 constexpr int kDkvSmem = 2 * kTile + kDkvStages * kTile + kStatSlots * 1024 + BwdSmem::kBarBytes + BwdSmem::kMisc;
 
 // BLK = 64: the KV block has 64 tokens (top half of the 128-row MMAs, lanes 64-127 idle) and one iteration
@@ -656,10 +662,10 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   }
   const uint32_t bar_base = smem_u32(bars);
   auto BAR = [&](int i) { return bar_base + (uint32_t)i * 8u; };
-  // kv_full, kv_empty, ring_full[NS], ring_empty[NS], s_full, dp_full, p_full, ds_full, fin, free
+  // kv_full, kv_empty, ring_full[NS], ring_empty[NS], s_full, dp_full, x_free, y_free, p_full, ds_full, fin, free
   constexpr int kKvFull = 0, kKvEmpty = 1, kRFull = 2, kREmpty = 2 + NS, kSFull = 2 + 2 * NS, kDpFull = kSFull + 1,
-                kPFull = kDpFull + 1, kDsFull = kPFull + 1, kFinal = kDsFull + 1, kFree = kFinal + 1,
-                kNumBars = kFree + 1;
+                kXFree = kDpFull + 1, kYFree = kXFree + 1, kPFull = kYFree + 1, kDsFull = kPFull + 1,
+                kFinal = kDsFull + 1, kFree = kFinal + 1, kNumBars = kFree + 1;
   static_assert(kNumBars <= 32, "barrier slots");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   WaitCtx wctx{&s_abort, p.status};
@@ -673,6 +679,8 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     }
     mbar_init(BAR(kSFull), 1);
     mbar_init(BAR(kDpFull), 1);
+    mbar_init(BAR(kXFree), 256);  // every compute thread holds its part of X (S^T, then dP^T) in registers
+    mbar_init(BAR(kYFree), 1);    // dV_i and dK_i have read P^T_i and dS^T_i from Y
     mbar_init(BAR(kPFull), 256);
     mbar_init(BAR(kDsFull), 256);
     mbar_init(BAR(kFinal), 2);
@@ -688,7 +696,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = s_tmem_base;
-  const uint32_t tS = tmem, tdP = tmem + 128u, tdV = tmem + 256u, tdK = tmem + 384u;
+  const uint32_t tX = tmem, tY = tmem + 128u, tdV = tmem + 256u, tdK = tmem + 384u;
   const int num_work = p.B * p.H * p.Nkv;
 
   constexpr int kPerIt = 128 / BLK;              // CSR entries per 128-row iteration
@@ -731,14 +739,15 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           if (!mbar_wait(BAR(kREmpty + stage), ph ^ 1, wctx, 501)) return false;
           if (lane == 0) {
             const CUtensorMap* tm = which ? &tm_do : &tm_q;
-            mbar_arrive_expect_tx(BAR(kRFull + stage), kTile + (which ? 0 : 1024));
+            mbar_arrive_expect_tx(BAR(kRFull + stage), kTile + (which ? 1024 : 0));
             for (int sl = 0; sl < 2; ++sl) {
               const uint32_t dst = smem_u32(sRing + stage * kTile + sl * kSlab);
               tma_load_4d(dst, tm, BAR(kRFull + stage), sl * 64, qa * BLK, h, b);
               if (BLK == 64) tma_load_4d(dst + 64 * 128, tm, BAR(kRFull + stage), sl * 64, qb * 64, h, b);
             }
-            if (!which) {
-              // row statistics of the query rows travel with their Q tile
+            if (which) {
+              // row statistics of the query rows travel with their dO tile: that stage is re-used only after
+              // dK of the tile two back, when the statistics slot of that tile is long free (two slots)
               float* st = sStats + (tile_cnt % kStatSlots) * 256;
               const long long plane = (long long)bh * ((long long)p.Nq * BLK);
               if (BLK == 128) {
@@ -776,15 +785,16 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (ok && pending >= 0) ok = load_pair(pending, pending);  // odd total: masked phantom second half
     }
   } else if (warp == kBwdMmaWarp || warp == kBwdMmaWarp + 1) {
-    // Two issuing warps (tcgen05.mma issue stalls the issuing thread at the execution rate, so a single
-    // issuer leaves the tensor pipe idle during its own barrier bookkeeping):
-    //   issuer 0: S^T_i = K Q_i^T and dV += P^T_i dO_i   (tensor-memory region S/P and dV)
-    //   issuer 1: dP^T_i = V dO_i^T and dK += dS^T_i Q_i (tensor-memory region dP/dS and dK)
+    // Two issuing warps, one per side of the compute threads:
+    //   issuer 0 (producer side): S^T_i = K Q_i^T and dP^T_i = V dO_i^T, alternately into X: each is issued as soon
+    //             as every compute thread has loaded the previous content of X into registers (x_free).
+    //   issuer 1 (consumer side): dV += P^T_i dO_i and dK += dS^T_i Q_i, reading P^T_i / dS^T_i from Y; its commit
+    //             after dK_i (which covers dV_i, earlier in program order) hands Y back to the compute threads.
     // Each issuer visits every ring position in increasing order (a parity wait is never more than one
     // phase behind) and every ring stage is released by one commit of each issuer.
     const int who = warp - kBwdMmaWarp;
     const uint32_t led = lane == 0;  // the whole warp runs the issue code, this lane issues
-    uint32_t r_cnt = 0, kv_cnt = 0, in_cnt = 0, free_cnt = 0;
+    uint32_t r_cnt = 0, kv_cnt = 0, in_cnt = 0, ds_cnt = 0, free_cnt = 0, x_cnt = 0;
     bool ok = true, first_item = true;
     const uint64_t k_desc = desc_k_major(smem_u32(sK)), v_desc = desc_k_major(smem_u32(sV));
     const uint64_t ring_k = desc_k_major(smem_u32(sRing)), ring_mn = desc_mn_major(smem_u32(sRing));
@@ -808,45 +818,39 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         return r;
       };
       if (who == 0) {
-        // ---- issuer 0
-        ok = wait_full(base);
-        if (ok) {
-          mma_ss_kk(tS, k_desc, ring_k + stage_of(base) * kTileDescStep, false, led);  // S^T_0
-          umma_commit_led(BAR(kSFull), led);
-          umma_commit_led(BAR(kREmpty + stage_of(base)), led);
-        }
-        __syncwarp();
-        for (int i = 0; i < T && ok; ++i) {
-          ok = wait_full(base + 2 * i + 1);  // dO_i
-          if (!ok) break;
-          PT_MARK(0)
-          ok = mbar_wait(BAR(kPFull), in_cnt & 1, wctx, 512);  // P^T_i in tensor memory
-          if (!ok) break;
-          PT_MARK(3)
-          ++in_cnt;
-          if (i == 0 && !first_item) {  // the previous item's epilogue has drained dV
-            ok = mbar_wait(BAR(kFree), free_cnt & 1, wctx, 513);
-            if (!ok) break;
+        // ---- issuer 0: the MMAs into X, in the order S^T_0, dP^T_0, S^T_1, dP^T_1, ...; before each of them
+        // (except the very first) the previous content of X must sit in registers
+        auto x_ready = [&]() -> bool {
+          if (x_cnt > 0) {
+            PT_MARK(0)
+            if (!mbar_wait(BAR(kXFree), (x_cnt - 1) & 1, wctx, 512)) return false;
+            PT_MARK(3)
           }
-          if (i == 0 && !first_item) ++free_cnt;
+          ++x_cnt;
           tc_fence_after();
+          return true;
+        };
+        for (int i = 0; i < T && ok; ++i) {
+          ok = wait_full(base + 2 * i);  // Q_i
+          if (ok) ok = x_ready();
+          if (!ok) break;
+          {
+            const uint32_t sq = stage_of(base + 2 * i);
+            mma_ss_kk(tX, k_desc, ring_k + sq * kTileDescStep, false, led);  // S^T_i
+            umma_commit_led(BAR(kSFull), led);
+            umma_commit_led(BAR(kREmpty + sq), led);
+          }
+          __syncwarp();
+          ok = wait_full(base + 2 * i + 1);  // dO_i
+          if (ok) ok = x_ready();
+          if (!ok) break;
           {
             const uint32_t sd = stage_of(base + 2 * i + 1);
-            mma_ts_kmn(tdV, tS, tS + 64u, ring_mn + sd * kTileDescStep, i > 0, led);  // dV += P^T dO_i
+            mma_ss_kk(tX, v_desc, ring_k + sd * kTileDescStep, false, led);  // dP^T_i
+            umma_commit_led(BAR(kDpFull), led);
             umma_commit_led(BAR(kREmpty + sd), led);
           }
           __syncwarp();
-          if (i + 1 < T) {
-            ok = wait_full(base + 2 * i + 2);  // Q_{i+1}
-            if (!ok) break;
-            {
-              const uint32_t sq = stage_of(base + 2 * i + 2);
-              mma_ss_kk(tS, k_desc, ring_k + sq * kTileDescStep, false, led);  // S^T_{i+1}, after dV_i in program order
-              umma_commit_led(BAR(kSFull), led);
-              umma_commit_led(BAR(kREmpty + sq), led);
-            }
-            __syncwarp();
-          }
         }
       } else {
         // ---- issuer 1
@@ -854,29 +858,34 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           ok = wait_full(base + 2 * i);  // Q_i (needed for dK_i; visited first to keep the waits in order)
           if (ok) ok = wait_full(base + 2 * i + 1);  // dO_i
           if (!ok) break;
+          PT_MARK(0)
+          ok = mbar_wait(BAR(kPFull), in_cnt & 1, wctx, 513);  // P^T_i in tensor memory
+          if (!ok) break;
+          PT_MARK(3)
+          ++in_cnt;
+          if (i == 0 && !first_item) {  // the previous item's epilogue has drained dV and dK
+            ok = mbar_wait(BAR(kFree), free_cnt & 1, wctx, 515);
+            if (!ok) break;
+            ++free_cnt;
+          }
+          tc_fence_after();
           {
             const uint32_t sd = stage_of(base + 2 * i + 1);
-            // dP^T_i: in program order after dK_{i-1}, which read dS^T_{i-1} from the same columns
-            mma_ss_kk(tdP, v_desc, ring_k + sd * kTileDescStep, false, led);
-            umma_commit_led(BAR(kDpFull), led);
+            mma_ts_kmn(tdV, tY, tY + 64u, ring_mn + sd * kTileDescStep, i > 0, led);  // dV += P^T dO_i
             umma_commit_led(BAR(kREmpty + sd), led);
           }
           __syncwarp();
           PT_MARK(0)
-          ok = mbar_wait(BAR(kDsFull), in_cnt & 1, wctx, 514);  // dS^T_i in tensor memory
+          ok = mbar_wait(BAR(kDsFull), ds_cnt & 1, wctx, 514);  // dS^T_i in tensor memory
           if (!ok) break;
           PT_MARK(4)
-          ++in_cnt;
-          if (i == 0 && !first_item) {  // the previous item's epilogue has drained dK
-            ok = mbar_wait(BAR(kFree), free_cnt & 1, wctx, 515);
-            if (!ok) break;
-          }
-          if (i == 0 && !first_item) ++free_cnt;
+          ++ds_cnt;
           tc_fence_after();
           {
             const uint32_t sq = stage_of(base + 2 * i);
-            mma_ts_kmn(tdK, tdP, tdP + 64u, ring_mn + sq * kTileDescStep, i > 0, led);  // dK += dS^T Q_i
+            mma_ts_kmn(tdK, tY + 32u, tY + 96u, ring_mn + sq * kTileDescStep, i > 0, led);  // dK += dS^T Q_i
             umma_commit_led(BAR(kREmpty + sq), led);
+            umma_commit_led(BAR(kYFree), led);
           }
           __syncwarp();
         }
@@ -897,7 +906,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const int row = threadIdx.x & 127;  // kv token inside the block = tensor-memory lane
     const bool row_active = (BLK == 128) || (row < 64);  // warp-uniform
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    uint32_t s_cnt = 0, dp_cnt = 0, fin_cnt = 0, tile_cnt = 0, r_cnt = 0;
+    uint32_t s_cnt = 0, dp_cnt = 0, fin_cnt = 0, tile_cnt = 0, r_cnt = 0, y_cnt = 0;
     bool ok = true;
     PT_DECL
     for (int band = 0; band * (int)gridDim.x < num_work && ok; ++band) {
@@ -929,24 +938,33 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const float4* st_l = reinterpret_cast<const float4*>(sStats + (tile_cnt % kStatSlots) * 256 + grp * 64);
         const float4* st_d = reinterpret_cast<const float4*>(sStats + (tile_cnt % kStatSlots) * 256 + 128 + grp * 64);
         ++tile_cnt;
-        // ---- phase 1: P^T = exp2(S^T*scale - lse[q]) -> bf16 -> tensor memory (head of this group's S half)
+        // ---- phase 1: P^T = exp2(S^T*scale - lse[q]) -> bf16 -> Y
         PT_MARK(0)
         ok = mbar_wait(BAR(kSFull), s_cnt & 1, wctx, 520);
         if (!ok) break;
         PT_MARK(1)
         ++s_cnt;
-        if (!row_active) {  // idle half of a 64-token block: barrier protocol only
+        if (!row_active) {
+          // idle half of a 64-token block: barrier protocol only, in exactly the order of the working threads
+          // (an arrival for the next phase of a 256-thread barrier must not precede the end of the running one)
+          mbar_arrive(BAR(kXFree));
+          if (y_cnt > 0) {
+            ok = mbar_wait(BAR(kYFree), (y_cnt - 1) & 1, wctx, 524);
+            if (!ok) break;
+          }
+          ++y_cnt;
           mbar_arrive(BAR(kPFull));
           ok = mbar_wait(BAR(kDpFull), dp_cnt & 1, wctx, 521);
           if (!ok) break;
           ++dp_cnt;
+          mbar_arrive(BAR(kXFree));
           mbar_arrive(BAR(kDsFull));
           continue;
         }
         {
-          // observe the arrival of this tile's row statistics directly (they were copied on the Q
-          // stage's barrier); the phase cannot have advanced further: the stage is held until dK
-          const uint32_t pos = base + 2 * (uint32_t)i;
+          // observe the arrival of this tile's row statistics directly (they were copied on the dO
+          // stage's barrier); the phase cannot have advanced further: the stage is held until dV
+          const uint32_t pos = base + 2 * (uint32_t)i + 1;
           ok = mbar_wait(BAR(kRFull + pos % NS), (pos / NS) & 1, wctx, 523);
           if (!ok) break;
         }
@@ -954,10 +972,13 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         float pr[64];
         {
           uint32_t* u = reinterpret_cast<uint32_t*>(pr);
-          tmem_ld32(tS + lane_base + grp * 64, u);
-          tmem_ld32(tS + lane_base + grp * 64 + 32, u + 32);
+          tmem_ld32(tX + lane_base + grp * 64, u);
+          tmem_ld32(tX + lane_base + grp * 64 + 32, u + 32);
           tmem_wait_ld();
         }
+        // S^T_i is in registers: X may take dP^T_i
+        tc_fence_before();
+        mbar_arrive(BAR(kXFree));
 #pragma unroll
         for (int c4 = 0; c4 < 16; ++c4) {
           const float4 l = st_l[c4];
@@ -971,26 +992,36 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
           for (int c = 0; c < 64; ++c) pr[c] = 0.f;
         }
+        // Y still feeds dV / dK of the tile before until their commit
+        if (y_cnt > 0) {
+          ok = mbar_wait(BAR(kYFree), (y_cnt - 1) & 1, wctx, 524);
+          if (!ok) break;
+        }
+        ++y_cnt;
+        tc_fence_after();
         {
           uint32_t pk[32];
 #pragma unroll
           for (int e = 0; e < 32; ++e) pk[e] = pack_bf16x2(pr[2 * e], pr[2 * e + 1]);
-          tmem_st32(tS + lane_base + grp * 64, pk);
+          tmem_st32(tY + lane_base + grp * 64, pk);
           tmem_wait_st();
         }
         tc_fence_before();
         mbar_arrive(BAR(kPFull));
         PT_MARK(2)
-        // ---- phase 2: dS^T = P^T o (dP^T - delta[q]) -> bf16 -> tensor memory
+        // ---- phase 2: dS^T = P^T o (dP^T - delta[q]) -> bf16 -> Y
         ok = mbar_wait(BAR(kDpFull), dp_cnt & 1, wctx, 521);
         if (!ok) break;
         PT_MARK(3)
         ++dp_cnt;
         tc_fence_after();
         uint32_t dp[64];
-        tmem_ld32(tdP + lane_base + grp * 64, dp);
-        tmem_ld32(tdP + lane_base + grp * 64 + 32, dp + 32);
+        tmem_ld32(tX + lane_base + grp * 64, dp);
+        tmem_ld32(tX + lane_base + grp * 64 + 32, dp + 32);
         tmem_wait_ld();
+        // dP^T_i is in registers: X may take S^T_{i+1}
+        tc_fence_before();
+        mbar_arrive(BAR(kXFree));
         {
           uint32_t pk[32];
 #pragma unroll
@@ -1003,7 +1034,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             pk[c4 * 2] = pack_bf16x2(d0, d1);
             pk[c4 * 2 + 1] = pack_bf16x2(d2, d3);
           }
-          tmem_st32(tdP + lane_base + grp * 64, pk);
+          tmem_st32(tY + lane_base + grp * 64 + 32, pk);
           tmem_wait_st();
         }
         tc_fence_before();
