@@ -662,9 +662,9 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   }
   const uint32_t bar_base = smem_u32(bars);
   auto BAR = [&](int i) { return bar_base + (uint32_t)i * 8u; };
-  // kv_full, kv_empty, ring_full[NS], ring_empty[NS], s_full, dp_full, x_free, y_free, p_full, ds_full, fin, free
+  // kv_full, kv_empty, ring_full[NS], ring_empty[NS], s_full, dp_full, x_free, y_free, ds_full, fin, free
   constexpr int kKvFull = 0, kKvEmpty = 1, kRFull = 2, kREmpty = 2 + NS, kSFull = 2 + 2 * NS, kDpFull = kSFull + 1,
-                kXFree = kDpFull + 1, kYFree = kXFree + 1, kPFull = kYFree + 1, kDsFull = kPFull + 1,
+                kXFree = kDpFull + 1, kYFree = kXFree + 1, kDsFull = kYFree + 1,
                 kFinal = kDsFull + 1, kFree = kFinal + 1, kNumBars = kFree + 1;
   static_assert(kNumBars <= 32, "barrier slots");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -680,8 +680,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     mbar_init(BAR(kSFull), 1);
     mbar_init(BAR(kDpFull), 1);
     mbar_init(BAR(kXFree), 256);  // every compute thread holds its part of X (S^T, then dP^T) in registers
-    mbar_init(BAR(kYFree), 1);    // dV_i and dK_i have read P^T_i and dS^T_i from Y
-    mbar_init(BAR(kPFull), 256);
+    mbar_init(BAR(kYFree), 2);    // dV_i and dK_i (one commit each) have read P^T_i and dS^T_i from Y
     mbar_init(BAR(kDsFull), 256);
     mbar_init(BAR(kFinal), 2);
     mbar_init(BAR(kFree), 256);
@@ -785,16 +784,19 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (ok && pending >= 0) ok = load_pair(pending, pending);  // odd total: masked phantom second half
     }
   } else if (warp == kBwdMmaWarp || warp == kBwdMmaWarp + 1) {
-    // Two issuing warps, one per side of the compute threads:
-    //   issuer 0 (producer side): S^T_i = K Q_i^T and dP^T_i = V dO_i^T, alternately into X: each is issued as soon
-    //             as every compute thread has loaded the previous content of X into registers (x_free).
-    //   issuer 1 (consumer side): dV += P^T_i dO_i and dK += dS^T_i Q_i, reading P^T_i / dS^T_i from Y; its commit
-    //             after dK_i (which covers dV_i, earlier in program order) hands Y back to the compute threads.
-    // Each issuer visits every ring position in increasing order (a parity wait is never more than one
-    // phase behind) and every ring stage is released by one commit of each issuer.
+    // Two issuing warps.  The tensor pipe executes MMAs in the order they were issued, whoever issued them, so the
+    // order decides what arrives late:
+    //   issuer 0: everything into X, alternately S^T_i = K Q_i^T and dP^T_i = V dO_i^T, each as soon as every compute
+    //             thread has loaded the previous content of X into registers (x_free); and dV += P^T_{i-1} dO_{i-1}
+    //             right BEHIND S^T_i, so that the dV MMAs never sit in front of the S^T the compute threads wait for
+    //             (P^T_{i-1} is complete by then: a compute thread stores it before it loads dP^T_{i-1}).
+    //   issuer 1: dK += dS^T_i Q_i.
+    // Y goes back to the compute threads when dV_i and dK_i have both completed (y_free, one commit each).
+    // Each issuer visits every ring position in increasing order (a parity wait is never more than one phase
+    // behind) and releases every stage once: by a commit after its last MMA on the tile, or by a plain arrival.
     const int who = warp - kBwdMmaWarp;
     const uint32_t led = lane == 0;  // the whole warp runs the issue code, this lane issues
-    uint32_t r_cnt = 0, kv_cnt = 0, in_cnt = 0, ds_cnt = 0, free_cnt = 0, x_cnt = 0;
+    uint32_t r_cnt = 0, kv_cnt = 0, ds_cnt = 0, free_cnt = 0, x_issued = 0, x_waited = 0;
     bool ok = true, first_item = true;
     const uint64_t k_desc = desc_k_major(smem_u32(sK)), v_desc = desc_k_major(smem_u32(sV));
     const uint64_t ring_k = desc_k_major(smem_u32(sRing)), ring_mn = desc_mn_major(smem_u32(sRing));
@@ -817,17 +819,32 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         PT_MARK(2)
         return r;
       };
+      auto wait_free = [&]() -> bool {  // the previous item's epilogue has drained the accumulators
+        if (first_item) return true;
+        const bool r = mbar_wait(BAR(kFree), free_cnt & 1, wctx, 515);
+        ++free_cnt;
+        return r;
+      };
       if (who == 0) {
-        // ---- issuer 0: the MMAs into X, in the order S^T_0, dP^T_0, S^T_1, dP^T_1, ...; before each of them
-        // (except the very first) the previous content of X must sit in registers
+        // ---- issuer 0.  Content number n of X (S^T and dP^T alternate) may be written once phases 0..n-1 of
+        // x_free have completed; the phases are waited for one by one, in order.
         auto x_ready = [&]() -> bool {
-          if (x_cnt > 0) {
-            PT_MARK(0)
-            if (!mbar_wait(BAR(kXFree), (x_cnt - 1) & 1, wctx, 512)) return false;
-            PT_MARK(3)
+          PT_MARK(0)
+          while (x_waited < x_issued) {
+            if (!mbar_wait(BAR(kXFree), x_waited & 1, wctx, 512)) return false;
+            ++x_waited;
           }
-          ++x_cnt;
+          PT_MARK(3)
           tc_fence_after();
+          return true;
+        };
+        auto issue_dv = [&](int i) -> bool {  // after x_ready() has seen dP^T_i consumed
+          if (i == 0 && !wait_free()) return false;
+          const uint32_t sd = stage_of(base + 2 * i + 1);
+          mma_ts_kmn(tdV, tY, tY + 64u, ring_mn + sd * kTileDescStep, i > 0, led);  // dV += P^T_i dO_i
+          umma_commit_led(BAR(kREmpty + sd), led);
+          umma_commit_led(BAR(kYFree), led);
+          __syncwarp();
           return true;
         };
         for (int i = 0; i < T && ok; ++i) {
@@ -839,8 +856,13 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             mma_ss_kk(tX, k_desc, ring_k + sq * kTileDescStep, false, led);  // S^T_i
             umma_commit_led(BAR(kSFull), led);
             umma_commit_led(BAR(kREmpty + sq), led);
+            ++x_issued;
           }
           __syncwarp();
+          if (i > 0) {
+            ok = issue_dv(i - 1);
+            if (!ok) break;
+          }
           ok = wait_full(base + 2 * i + 1);  // dO_i
           if (ok) ok = x_ready();
           if (!ok) break;
@@ -848,38 +870,29 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             const uint32_t sd = stage_of(base + 2 * i + 1);
             mma_ss_kk(tX, v_desc, ring_k + sd * kTileDescStep, false, led);  // dP^T_i
             umma_commit_led(BAR(kDpFull), led);
-            umma_commit_led(BAR(kREmpty + sd), led);
+            ++x_issued;
           }
           __syncwarp();
         }
+        if (ok) ok = x_ready();  // dP^T of the last tile is in registers, so its P^T is complete
+        if (ok) ok = issue_dv(T - 1);
       } else {
         // ---- issuer 1
         for (int i = 0; i < T && ok; ++i) {
-          ok = wait_full(base + 2 * i);  // Q_i (needed for dK_i; visited first to keep the waits in order)
-          if (ok) ok = wait_full(base + 2 * i + 1);  // dO_i
+          ok = wait_full(base + 2 * i);  // Q_i
+          if (ok) ok = wait_full(base + 2 * i + 1);  // dO_i: not read here, released by a plain arrival
           if (!ok) break;
-          PT_MARK(0)
-          ok = mbar_wait(BAR(kPFull), in_cnt & 1, wctx, 513);  // P^T_i in tensor memory
-          if (!ok) break;
-          PT_MARK(3)
-          ++in_cnt;
-          if (i == 0 && !first_item) {  // the previous item's epilogue has drained dV and dK
-            ok = mbar_wait(BAR(kFree), free_cnt & 1, wctx, 515);
-            if (!ok) break;
-            ++free_cnt;
-          }
-          tc_fence_after();
-          {
-            const uint32_t sd = stage_of(base + 2 * i + 1);
-            mma_ts_kmn(tdV, tY, tY + 64u, ring_mn + sd * kTileDescStep, i > 0, led);  // dV += P^T dO_i
-            umma_commit_led(BAR(kREmpty + sd), led);
-          }
+          if (led) mbar_arrive(BAR(kREmpty + stage_of(base + 2 * i + 1)));
           __syncwarp();
           PT_MARK(0)
           ok = mbar_wait(BAR(kDsFull), ds_cnt & 1, wctx, 514);  // dS^T_i in tensor memory
           if (!ok) break;
           PT_MARK(4)
           ++ds_cnt;
+          if (i == 0 && !wait_free()) {
+            ok = false;
+            break;
+          }
           tc_fence_after();
           {
             const uint32_t sq = stage_of(base + 2 * i);
@@ -953,7 +966,6 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             if (!ok) break;
           }
           ++y_cnt;
-          mbar_arrive(BAR(kPFull));
           ok = mbar_wait(BAR(kDpFull), dp_cnt & 1, wctx, 521);
           if (!ok) break;
           ++dp_cnt;
@@ -1004,10 +1016,8 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
           for (int e = 0; e < 32; ++e) pk[e] = pack_bf16x2(pr[2 * e], pr[2 * e + 1]);
           tmem_st32(tY + lane_base + grp * 64, pk);
-          tmem_wait_st();
+          tmem_wait_st();  // P^T is complete before this thread reports dP^T consumed (the signal dV follows)
         }
-        tc_fence_before();
-        mbar_arrive(BAR(kPFull));
         PT_MARK(2)
         // ---- phase 2: dS^T = P^T o (dP^T - delta[q]) -> bf16 -> Y
         ok = mbar_wait(BAR(kDpFull), dp_cnt & 1, wctx, 521);
