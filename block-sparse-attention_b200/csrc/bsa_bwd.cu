@@ -1,7 +1,8 @@
 // Block-sparse attention backward for sm_100a (BF16, MHA, D = 128, 128-token blocks).
 //
 // Three launches, no atomics anywhere, every accumulation in a fixed order (bit-reproducible):
-//   1. preprocess : delta[row] = sum_d O*dO, lse_log2[row] = lse*log2(e) (+inf for empty rows so that
+//   1. preprocess : delta[row] = -sum_d O*dO, lse_log2[row] = -lse*log2(e), both stored NEGATED so that the main
+//                   kernels add them with packed fp32x2 instructions (-inf for empty rows so that
 //                   the recomputed probabilities are exactly 0), both padded to whole 128-row tiles
 //   2. dQ kernel  : one work item per query tile, driven by the q2k index.  Per selected KV block:
 //                   S = Q K^T, dP = dO V^T, P = exp2(S*scale - lse), dS = P o (dP - delta) (bf16, back to
@@ -65,8 +66,8 @@ struct BwdParams {
   const int32_t* __restrict__ order_kv;
   const int32_t* __restrict__ block_sizes;  // optional valid-token counts of the KV blocks
   long long bs_stride_b, bs_stride_h;
-  const float* __restrict__ lse_log2;  // [B,H,Nq*128]
-  const float* __restrict__ delta;     // [B,H,Nq*128]
+  const float* __restrict__ lse_log2;  // [B,H,Nq*128]  -lse * log2(e)
+  const float* __restrict__ delta;     // [B,H,Nq*128]  -sum_d O dO
   __nv_bfloat16* dq;
   __nv_bfloat16* dk;
   __nv_bfloat16* dv;
@@ -133,8 +134,8 @@ bwd_preprocess_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* 
         const float lv = lse[bh * Sq + s];
         l = (lv == -INFINITY) ? INFINITY : lv * kLog2e;
       }
-      delta[bh * SqPad + s] = acc;
-      lse_log2[bh * SqPad + s] = l;
+      delta[bh * SqPad + s] = -acc;
+      lse_log2[bh * SqPad + s] = -l;
     }
   }
 }
@@ -527,8 +528,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         continue;
       }
       const long long srow = ((long long)b * p.H + h) * ((long long)p.Nq * BLK) + seq;
-      const float lse2 = row_active ? p.lse_log2[srow] : INFINITY;
-      const float dlt = row_active ? p.delta[srow] : 0.f;
+      const float nlse = row_active ? p.lse_log2[srow] : -INFINITY;  // negated statistics, see the preprocess
+      const float ndlt = row_active ? p.delta[srow] : 0.f;
+      const uint64_t sc2 = pack2(p.scale_log2, p.scale_log2), nl2 = pack2(nlse, nlse), nd2 = pack2(ndlt, ndlt);
       const int32_t* idx_row = p.q2k_index + (long long)w * p.cap;
       // valid kv tokens among this group's 64 columns of the 128-token tile of iteration j; fetched one iteration
       // ahead so that the index load never sits in front of the arithmetic
@@ -566,10 +568,12 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         tc_fence_before();
         mbar_arrive(BAR(kSFree));  // S_j is in registers: the next S may be computed
         if (j + 1 < n) len_next = valid_len(j + 1);
-        const float neg_l = -lse2;
 #pragma unroll
-        for (int c = 0; c < 64; c += 2)
-          exp2_pair(c >> 1, fmaf(pr[c], p.scale_log2, neg_l), fmaf(pr[c + 1], p.scale_log2, neg_l), pr[c], pr[c + 1]);
+        for (int c = 0; c < 64; c += 2) {
+          float x0, x1;
+          unpack2(ffma2(pack2(pr[c], pr[c + 1]), sc2, nl2), x0, x1);
+          exp2_pair(c >> 1, x0, x1, pr[c], pr[c + 1]);
+        }
         if (len < 64) {
 #pragma unroll
           for (int c = 0; c < 64; ++c) pr[c] = (c < len) ? pr[c] : 0.f;
@@ -590,8 +594,9 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           uint32_t pk[32];
 #pragma unroll
           for (int e = 0; e < 32; ++e) {
-            const float d0 = pr[2 * e] * (__uint_as_float(dp[2 * e]) - dlt);
-            const float d1 = pr[2 * e + 1] * (__uint_as_float(dp[2 * e + 1]) - dlt);
+            float d0, d1;
+            unpack2(fmul2(pack2(pr[2 * e], pr[2 * e + 1]),
+                          fadd2(pack2(__uint_as_float(dp[2 * e]), __uint_as_float(dp[2 * e + 1])), nd2)), d0, d1);
             pk[e] = pack_bf16x2(d0, d1);
           }
           tmem_st32(tbuf, pk);
@@ -920,6 +925,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const bool row_active = (BLK == 128) || (row < 64);  // warp-uniform
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
     uint32_t s_cnt = 0, dp_cnt = 0, fin_cnt = 0, tile_cnt = 0, r_cnt = 0, y_cnt = 0;
+    const uint64_t sc2 = pack2(p.scale_log2, p.scale_log2);
     bool ok = true;
     PT_DECL
     for (int band = 0; band * (int)gridDim.x < num_work && ok; ++band) {
@@ -993,11 +999,12 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         mbar_arrive(BAR(kXFree));
 #pragma unroll
         for (int c4 = 0; c4 < 16; ++c4) {
-          const float4 l = st_l[c4];
-          exp2_pair(2 * c4, fmaf(pr[c4 * 4 + 0], p.scale_log2, -l.x), fmaf(pr[c4 * 4 + 1], p.scale_log2, -l.y),
-                    pr[c4 * 4 + 0], pr[c4 * 4 + 1]);
-          exp2_pair(2 * c4 + 1, fmaf(pr[c4 * 4 + 2], p.scale_log2, -l.z), fmaf(pr[c4 * 4 + 3], p.scale_log2, -l.w),
-                    pr[c4 * 4 + 2], pr[c4 * 4 + 3]);
+          const float4 l = st_l[c4];  // negated
+          float x0, x1, x2, x3;
+          unpack2(ffma2(pack2(pr[c4 * 4 + 0], pr[c4 * 4 + 1]), sc2, pack2(l.x, l.y)), x0, x1);
+          unpack2(ffma2(pack2(pr[c4 * 4 + 2], pr[c4 * 4 + 3]), sc2, pack2(l.z, l.w)), x2, x3);
+          exp2_pair(2 * c4, x0, x1, pr[c4 * 4 + 0], pr[c4 * 4 + 1]);
+          exp2_pair(2 * c4 + 1, x2, x3, pr[c4 * 4 + 2], pr[c4 * 4 + 3]);
         }
         // masked KV token, or the phantom second half of an odd pair
         if (!kv_live || (BLK == 64 && grp == 1 && 2 * i + 1 >= entries)) {
@@ -1036,11 +1043,14 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           uint32_t pk[32];
 #pragma unroll
           for (int c4 = 0; c4 < 16; ++c4) {
-            const float4 d = st_d[c4];
-            const float d0 = pr[c4 * 4 + 0] * (__uint_as_float(dp[c4 * 4 + 0]) - d.x);
-            const float d1 = pr[c4 * 4 + 1] * (__uint_as_float(dp[c4 * 4 + 1]) - d.y);
-            const float d2 = pr[c4 * 4 + 2] * (__uint_as_float(dp[c4 * 4 + 2]) - d.z);
-            const float d3 = pr[c4 * 4 + 3] * (__uint_as_float(dp[c4 * 4 + 3]) - d.w);
+            const float4 d = st_d[c4];  // negated
+            float d0, d1, d2, d3;
+            unpack2(fmul2(pack2(pr[c4 * 4 + 0], pr[c4 * 4 + 1]),
+                          fadd2(pack2(__uint_as_float(dp[c4 * 4 + 0]), __uint_as_float(dp[c4 * 4 + 1])), pack2(d.x, d.y))),
+                    d0, d1);
+            unpack2(fmul2(pack2(pr[c4 * 4 + 2], pr[c4 * 4 + 3]),
+                          fadd2(pack2(__uint_as_float(dp[c4 * 4 + 2]), __uint_as_float(dp[c4 * 4 + 3])), pack2(d.z, d.w))),
+                    d2, d3);
             pk[c4 * 2] = pack_bf16x2(d0, d1);
             pk[c4 * 2 + 1] = pack_bf16x2(d2, d3);
           }
