@@ -1022,8 +1022,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           uint32_t pk[32];
 #pragma unroll
           for (int e = 0; e < 32; ++e) pk[e] = pack_bf16x2(pr[2 * e], pr[2 * e + 1]);
-          tmem_st32(tY + lane_base + grp * 64, pk);
-          tmem_wait_st();  // P^T is complete before this thread reports dP^T consumed (the signal dV follows)
+          tmem_st32(tY + lane_base + grp * 64, pk);  // completion is awaited below, under the dP^T load
         }
         PT_MARK(2)
         // ---- phase 2: dS^T = P^T o (dP^T - delta[q]) -> bf16 -> Y
@@ -1036,7 +1035,9 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         tmem_ld32(tX + lane_base + grp * 64, dp);
         tmem_ld32(tX + lane_base + grp * 64 + 32, dp + 32);
         tmem_wait_ld();
-        // dP^T_i is in registers: X may take S^T_{i+1}
+        // dP^T_i is in registers: X may take S^T_{i+1}.  P^T must be complete before this thread says so: the
+        // dV MMAs follow this signal.
+        tmem_wait_st();
         tc_fence_before();
         mbar_arrive(BAR(kXFree));
         {
