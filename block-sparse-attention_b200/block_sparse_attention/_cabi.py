@@ -120,6 +120,7 @@ SIGNATURES = {
     "bsa_abi_version": (ctypes.c_int, []),
     "bsa_last_error": (ctypes.c_char_p, []),
     "bsa_num_sms": (ctypes.c_int, [ctypes.c_int]),
+    "bsa_selftest_wait": (ctypes.c_int, [ctypes.c_uint64, _vp, _vp, _vp]),
     "bsa_fwd": (ctypes.c_int, [ctypes.POINTER(FwdArgs), _vp]),
     "bsa_fwd_combine": (ctypes.c_int, [_vp, _vp, _vp, _vp, _i32, _i32, _i32, _i32, _i32,
                                        ctypes.POINTER(ctypes.c_int64), _vp]),

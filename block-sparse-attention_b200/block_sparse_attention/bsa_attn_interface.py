@@ -101,9 +101,89 @@ def _sm100_blk64_auto_kv_splits(q: torch.Tensor, q2k_block_index: torch.Tensor, 
     return _sm100_blk64_kv_splits_from_count(kv_blocks, max_kv_splits)
 
 
-def choose_blk64_use_clc(*_args, **_kwargs) -> bool:
-    """Kept for signature compatibility.  The engine has a single persistent scheduler; there is no
-    hardware work-stealing mode to choose, so the answer is always False."""
+def _sm100_blk64_auto_fp8_kv_splits(kv_blocks: int, heads: int, seqlen_q: int, batch: int, num_sms: int) -> int:
+    """Automatic split count of the Sage FP8 64-token forward (reference bsa_attn_interface.py:693-718,
+    table in its tests/test_bsa_fp8_fwd.py:17-66).  The kernel runs one persistent CTA per SM, so splitting
+    the KV range only pays when the query tiles alone leave SMs idle: the count doubles while twice as
+    many (tile, split) items still fit the SMs, up to 16, and is halved again until every split keeps at
+    least 8 blocks (two splits: at least 128 blocks in total).  ``kv_blocks`` is the largest per-tile
+    block count."""
+    kv_blocks, num_sms = int(kv_blocks), int(num_sms)
+    tiles = int(batch) * int(heads) * _ceil_div(int(seqlen_q), 64)
+    if tiles >= num_sms:
+        return 1
+    splits = 1
+    while splits < 16 and 2 * splits * tiles <= num_sms:
+        splits *= 2
+    while splits > 1:
+        enough = kv_blocks >= 8 * splits and not (splits == 2 and kv_blocks < 128)
+        if enough:
+            break
+        splits //= 2
+    return splits
+
+
+def _build_sm100_blk64_kv_split_offsets(q2k_block_nums: Optional[torch.Tensor], uniform_block_sparse_num: int,
+                                        batch_size: int, num_heads: int, num_q_blocks: int, kv_splits: int,
+                                        device: torch.device) -> torch.Tensor:
+    """Split boundaries ``[B, H, Nq, kv_splits + 1]`` (int32, in 64-token blocks) of the 64-token forward.
+
+    The reference builds this tensor on the host and hands it to its kernel (bsa_attn_interface.py:779-823,
+    8-block-aligned because its kernel consumes eight blocks per step).  Here the kernel derives the
+    boundaries itself from the row count - split ``s`` takes KV iterations ``[n*s/k, n*(s+1)/k)`` of the
+    row's ``n = ceil(count / 2)`` two-block iterations - so no tensor is needed on the hot path; this
+    function returns exactly those boundaries for callers and tests that want to see them."""
+    assert 1 <= kv_splits <= 256, "kv_splits must be in [1, 256]"
+    if q2k_block_nums is not None and q2k_block_nums.numel() > 0:
+        counts = q2k_block_nums.to(device=device, dtype=torch.int64).clamp_min(0)
+    else:
+        counts = torch.full((batch_size, num_heads, num_q_blocks), int(uniform_block_sparse_num),
+                            dtype=torch.int64, device=device)
+    iters = (counts + 1) // 2
+    s = torch.arange(kv_splits + 1, dtype=torch.int64, device=device)
+    bounds = 2 * ((iters[..., None] * s) // kv_splits)
+    return torch.minimum(bounds, counts[..., None]).to(torch.int32).contiguous()
+
+
+def _blk64_split_workspace_bytes(q: torch.Tensor, value_dim: int, kv_splits: int) -> int:
+    """Bytes a split run keeps alive: FP32 partial O and LSE of every split plus the final output and LSE."""
+    batch, heads, seqlen_q, _ = q.shape
+    rows = batch * heads * seqlen_q
+    return int(kv_splits * rows * (value_dim + 1) * 4 + rows * (value_dim * q.element_size() + 4))
+
+
+def _resolve_blk64_split_workspace(q: torch.Tensor, value_dim: int, kv_splits: int, allow_fallback: bool) -> int:
+    """Fits the split count to the memory that can still be allocated (reference bsa_attn_interface.py:841-873):
+    free device memory plus what the caching allocator holds unused, minus a reserve of 5 % of the device
+    (at least 512 MiB).  An automatic count is halved until it fits; an explicit one raises RuntimeError."""
+    kv_splits = int(kv_splits)
+    if kv_splits <= 1 or not q.is_cuda:
+        return kv_splits
+    free_bytes, total_bytes = torch.cuda.mem_get_info(q.device)
+    cached = max(0, torch.cuda.memory_reserved(q.device) - torch.cuda.memory_allocated(q.device))
+    budget = max(0, free_bytes + cached - max(512 << 20, int(0.05 * total_bytes)))
+    fit = kv_splits
+    while fit > 1:
+        need = _blk64_split_workspace_bytes(q, value_dim, fit)
+        if need <= budget:
+            return fit
+        if not allow_fallback:
+            raise RuntimeError(
+                f"blk64 split-KV kv_splits={kv_splits} requires about {need / (1 << 30):.2f} GiB of live "
+                f"workspace, but only {budget / (1 << 30):.2f} GiB is available after the safety reserve; "
+                "lower kv_splits")
+        fit //= 2
+    return 1
+
+
+def choose_blk64_use_clc(q: torch.Tensor, block_sparse_num: int, q2k_block_nums: Optional[torch.Tensor] = None,
+                         layout: str = "bhsd") -> bool:
+    """Same signature as the reference's scheduler chooser (bsa_attn_interface.py:2061-2066), which picks
+    between its static and its hardware work-stealing (CLC) launch.  This engine has one scheduler - a
+    persistent grid walking a longest-first work list - so there is nothing to choose and the answer is
+    always False; ``use_clc`` is accepted by ``bsa_attn_fwd`` and has no effect."""
+    assert layout in ("bhsd", "bshd"), f"layout must be 'bhsd' or 'bshd', got {layout!r}"
+    assert q.dim() == 4
     return False
 
 
@@ -282,7 +362,8 @@ def bsa_attn_fwd(
     (``count`` = ``q2k_block_nums[b,h,m]`` or ``block_sparse_num``), ``block_sizes`` masks the tail tokens
     of KV blocks, rows with no live block give ``out = 0`` and ``lse = -inf``, LSE is the natural log of
     the scaled scores' partition sum and is returned iff ``return_lse``, a gradient is required or an
-    ``lse`` buffer was passed.  BF16 (FP16 with 128-token blocks); D = 128, or 64 / 96 with 128-token blocks
+    ``lse`` buffer was passed.  ``block_sizes`` may have rank 1 ``(Nkv,)``, 2 ``(B, Nkv)`` or 3 ``(B, Hkv, Nkv)``
+    for both block sizes.  BF16 (FP16 with 128-token blocks); D = 128, or 64 / 96 with 128-token blocks
     (those ride on the 128-wide tiles: the tensor maps zero-fill the missing channels).  Relaxations over the reference: odd fixed counts are
     accepted for 128-token blocks and the physical KV tail is always masked.
     """
@@ -344,7 +425,7 @@ def bsa_attn_fwd(
         assert block_sparse_num >= 1, f"block_sparse_num={block_sparse_num} must be >= 1"
         assert q2k_block_index.shape[-1] >= block_sparse_num, (
             f"q2k_block_index last dim ({q2k_block_index.shape[-1]}) must be >= block_sparse_num ({block_sparse_num})")
-    bs_strides = _block_size_strides(block_sizes, B, Hkv, Nkv, (1,) if blk == 128 else (1, 2, 3))
+    bs_strides = _block_size_strides(block_sizes, B, Hkv, Nkv, (1, 2, 3))
     if softmax_scale is None:
         softmax_scale = 1.0 / math.sqrt(D)
 
@@ -372,6 +453,7 @@ def bsa_attn_fwd(
         else:
             splits = int(kv_splits)
         splits = max(1, min(splits, 256))
+        splits = _resolve_blk64_split_workspace(qb, D, splits, allow_fallback=isinstance(kv_splits, str))
 
     _launch_fwd(q=qb, k=kb, v=vb, out=out_b, lse=lse_buf, q2k_block_index=q2k_block_index,
                 q2k_block_nums=q2k_block_nums, block_sizes=block_sizes, bs_strides=bs_strides, blk=blk,
@@ -464,9 +546,18 @@ def bsa_fp8_blk64_fwd(
 ) -> torch.Tensor:
     """Sage FP8 forward with 64-token blocks (reference bsa_attn_interface.py:2953-3182): same scale
     recipe and metadata as the 128-block entry; returns one BF16 BHSD tensor.  The split count is chosen
-    here (one split; the reference's automatic FP8 split policy targets its own kernel's occupancy)."""
+    here by the reference's automatic FP8 policy (``_sm100_blk64_auto_fp8_kv_splits``) from the row width of
+    the index, so a short-Q call that cannot fill the SMs with query tiles is split over the KV range; no
+    device value is read back."""
+    assert q_fp8.is_cuda and q_fp8.dim() == 4
+    B, H, Sq, _ = q_fp8.shape
+    has_nums = q2k_block_nums is not None and q2k_block_nums.numel() > 0
+    width = int(q2k_block_index.shape[-1]) if has_nums else int(topk_num)
+    num_sms = int(_cabi.load().bsa_num_sms(q_fp8.device.index or 0))
+    splits = _sm100_blk64_auto_fp8_kv_splits(width, H, Sq, B, num_sms)
+    splits = _resolve_blk64_split_workspace(q_fp8, 128, splits, allow_fallback=True)
     return _bsa_fp8_blk128_fwd(q_fp8, k_fp8, v_fp8, q_sfs, k_sfs, v_sfs, q2k_block_index, topk_num,
-                               softmax_scale, block_sizes, q2k_block_nums, 1, blk=64)
+                               softmax_scale, block_sizes, q2k_block_nums, splits, blk=64)
 
 
 def bsa_fp8_fwd(

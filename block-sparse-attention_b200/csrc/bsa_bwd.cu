@@ -18,15 +18,18 @@
 // to bf16 before the dV/dK/dQ GEMMs :1766, :1808-1809; dK and dQ scaled by softmax_scale at the end
 // :1864, :2351), its preprocess csrc/bwd/bsa_bwd_preprocess.py:184-324 and its CSR walk :86-112.
 //
-// Warp roles (both kernels): warps 0-7 compute (two groups of 128 threads, thread = tensor-memory lane,
-// group g owns columns [64g, 64g+64) of the score tiles), warps 8-9 MMA issue, warp 10 TMA producer.
-#include "../../include/bsa_b200.h"
+// Warp roles: warps 0-7 compute in both kernels (two groups of 128 threads, thread = tensor-memory lane, group g
+// owns columns [64g, 64g+64) of the score tiles).  dQ kernel (384 threads): warps 8, 9 and 10 issue the MMAs of
+// one dependency chain each (S, dQ, dP), warp 11 is the TMA producer.  dK/dV kernel (352 threads): warps 8 and 9
+// issue MMAs, warp 10 is the TMA producer.
+#include "bsa_b200.h"
 #include "bsa_common.cuh"
 #include "bsa_host.h"
 
 #ifdef BSA_PHASE_TIMERS
-__device__ unsigned long long g_bwd_prof[128];
-#define PTB_FLUSH(base) PT_FLUSH_TO(g_bwd_prof, base)
+// Development builds only (build.py --phase-timers): per-role clock counters, read by bsa_bwd_phase_timers().
+__device__ unsigned long long g_bwd_phase[128];
+#define PTB_FLUSH(base) PT_FLUSH_TO(g_bwd_phase, base)
 #else
 #define PTB_FLUSH(base)
 #endif
@@ -174,34 +177,6 @@ __device__ __forceinline__ void store_row_half(__nv_bfloat16* dst, const uint32_
     v.z = pack_bf16x2(__uint_as_float(acc[ch * 8 + 4]) * scale, __uint_as_float(acc[ch * 8 + 5]) * scale);
     v.w = pack_bf16x2(__uint_as_float(acc[ch * 8 + 6]) * scale, __uint_as_float(acc[ch * 8 + 7]) * scale);
     reinterpret_cast<uint4*>(dst)[ch] = v;
-  }
-}
-
-// Of every four column pairs of a probability row, this many take the polynomial exp2 on the FMA pipe
-// instead of the special-function unit.  Both compute groups of a kernel recompute their 64 columns at the
-// same time on the same four schedulers, so the phase is bound by the special-function unit (16 results
-// per clock per SM) unless a share of it moves to the FMA pipe.
-#ifndef BSA_BWD_EX2_EMU4
-#define BSA_BWD_EX2_EMU4 0
-#endif
-
-// 1 recomputes the probabilities with the packed half-precision exp2 (two results per special-function
-// operation).  Measured on B200 (cfg2 backward): 13.4 ms against 13.1 ms with the fp32 instruction - the
-// conversions to and from half precision cost what the unit saves, and the phase is bound by its tensor-memory
-// round trips (870 of its 1500 clocks remain with no exponential at all) - so it is off.
-#ifndef BSA_BWD_EX2_F16
-#define BSA_BWD_EX2_F16 0
-#endif
-
-// exp2 of two scaled-and-shifted scores (pair index `pair` selects the unit that computes them)
-__device__ __forceinline__ void exp2_pair(int pair, float x0, float x1, float& y0, float& y1) {
-  if (BSA_BWD_EX2_F16) {
-    unpack_f16x2(ex2_f16x2(pack_f16x2(x0, x1)), y0, y1);
-  } else if ((pair & 3) < BSA_BWD_EX2_EMU4) {
-    unpack2(ex2_emu2(x0, x1), y0, y1);
-  } else {
-    y0 = ex2_approx(x0);
-    y1 = ex2_approx(x1);
   }
 }
 
@@ -572,7 +547,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
         for (int c = 0; c < 64; c += 2) {
           float x0, x1;
           unpack2(ffma2(pack2(pr[c], pr[c + 1]), sc2, nl2), x0, x1);
-          exp2_pair(c >> 1, x0, x1, pr[c], pr[c + 1]);
+          pr[c] = ex2_approx(x0);
+          pr[c + 1] = ex2_approx(x1);
         }
         if (len < 64) {
 #pragma unroll
@@ -636,14 +612,19 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 // ------------------------------------------------------------------------------------------------
 // 3. dK/dV kernel
 // ------------------------------------------------------------------------------------------------
-// smem: K | V | ring of 5 tiles (Q_i, dO_i alternating) | row statistics [2][2][128] f32 | barriers | misc
+// smem: K | V | ring of 5 tiles (Q_i, dO_i alternating) | row statistics: lse [3][128], delta [2][128] f32 |
+// barriers | misc.  The lse row of a query tile travels with its Q stage and the delta row with its dO stage, so
+// the exponentials of a tile wait for nothing but S^T.
 // Tensor memory: X @0 takes S^T_i and, once every compute thread holds S^T_i in registers, dP^T_i; once that is
 // in registers too, S^T_{i+1}.  Y @128 takes P^T_i and dS^T_i (bf16, 32 columns each per compute group), the
 // tensor-memory operands of dV @256 += P^T dO and dK @384 += dS^T Q.  No MMA result that iteration i+1 needs waits
 // for an MMA that consumes what the compute threads produce in iteration i.
 constexpr int kDkvStages = 5;
-constexpr int kStatSlots = 2;
-constexpr int kDkvSmem = 2 * kTile + kDkvStages * kTile + kStatSlots * 1024 + BwdSmem::kBarBytes + BwdSmem::kMisc;
+// lse_{i+3} is loaded into the stage that dV_i releases, i.e. after the compute threads have finished with lse_i:
+// three slots; delta_{i+2} into the stage that dK_i releases: two slots.
+constexpr int kLseSlots = 3, kDeltaSlots = 2;
+constexpr int kStatBytes = (kLseSlots + kDeltaSlots) * 512;
+constexpr int kDkvSmem = 2 * kTile + kDkvStages * kTile + kStatBytes + BwdSmem::kBarBytes + BwdSmem::kMisc;
 
 // BLK = 64: the KV block has 64 tokens (top half of the 128-row MMAs, lanes 64-127 idle) and one iteration
 // covers two CSR entries: their 64-row Q / dO tiles form one 128-row ring tile, so compute group g owns
@@ -657,8 +638,9 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   uint8_t* sK = smem_raw;
   uint8_t* sV = sK + kTile;
   uint8_t* sRing = sV + kTile;
-  float* sStats = reinterpret_cast<float*>(sRing + NS * kTile);  // [slot][0: lse_log2, 1: delta][128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sStats) + kStatSlots * 1024);
+  float* sLse = reinterpret_cast<float*>(sRing + NS * kTile);  // [kLseSlots][128]  -lse * log2(e)
+  float* sDelta = sLse + kLseSlots * 128;                        // [kDeltaSlots][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sLse) + kStatBytes);
   uint32_t& s_tmem_base = *reinterpret_cast<uint32_t*>(bars + 32);
   volatile int& s_abort = *reinterpret_cast<volatile int*>(bars + 33);
   if ((smem_u32(smem_raw) & 1023u) != 0) {
@@ -743,26 +725,20 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           if (!mbar_wait(BAR(kREmpty + stage), ph ^ 1, wctx, 501)) return false;
           if (lane == 0) {
             const CUtensorMap* tm = which ? &tm_do : &tm_q;
-            mbar_arrive_expect_tx(BAR(kRFull + stage), kTile + (which ? 1024 : 0));
+            mbar_arrive_expect_tx(BAR(kRFull + stage), kTile + 512);
             for (int sl = 0; sl < 2; ++sl) {
               const uint32_t dst = smem_u32(sRing + stage * kTile + sl * kSlab);
               tma_load_4d(dst, tm, BAR(kRFull + stage), sl * 64, qa * BLK, h, b);
               if (BLK == 64) tma_load_4d(dst + 64 * 128, tm, BAR(kRFull + stage), sl * 64, qb * 64, h, b);
             }
-            if (which) {
-              // row statistics of the query rows travel with their dO tile: that stage is re-used only after
-              // dK of the tile two back, when the statistics slot of that tile is long free (two slots)
-              float* st = sStats + (tile_cnt % kStatSlots) * 256;
-              const long long plane = (long long)bh * ((long long)p.Nq * BLK);
-              if (BLK == 128) {
-                bulk_load_1d(smem_u32(st), p.lse_log2 + plane + (long long)qa * 128, 512, BAR(kRFull + stage));
-                bulk_load_1d(smem_u32(st + 128), p.delta + plane + (long long)qa * 128, 512, BAR(kRFull + stage));
-              } else {
-                bulk_load_1d(smem_u32(st), p.lse_log2 + plane + (long long)qa * 64, 256, BAR(kRFull + stage));
-                bulk_load_1d(smem_u32(st + 64), p.lse_log2 + plane + (long long)qb * 64, 256, BAR(kRFull + stage));
-                bulk_load_1d(smem_u32(st + 128), p.delta + plane + (long long)qa * 64, 256, BAR(kRFull + stage));
-                bulk_load_1d(smem_u32(st + 192), p.delta + plane + (long long)qb * 64, 256, BAR(kRFull + stage));
-              }
+            // row statistics of the query rows: lse with the Q tile, delta with the dO tile
+            float* st = which ? sDelta + (tile_cnt % kDeltaSlots) * 128 : sLse + (tile_cnt % kLseSlots) * 128;
+            const float* src = (which ? p.delta : p.lse_log2) + (long long)bh * ((long long)p.Nq * BLK);
+            if (BLK == 128) {
+              bulk_load_1d(smem_u32(st), src + (long long)qa * 128, 512, BAR(kRFull + stage));
+            } else {
+              bulk_load_1d(smem_u32(st), src + (long long)qa * 64, 256, BAR(kRFull + stage));
+              bulk_load_1d(smem_u32(st + 64), src + (long long)qb * 64, 256, BAR(kRFull + stage));
             }
           }
           ++r_cnt;
@@ -954,8 +930,8 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         continue;
       }
       for (int i = 0; i < T && ok; ++i) {
-        const float4* st_l = reinterpret_cast<const float4*>(sStats + (tile_cnt % kStatSlots) * 256 + grp * 64);
-        const float4* st_d = reinterpret_cast<const float4*>(sStats + (tile_cnt % kStatSlots) * 256 + 128 + grp * 64);
+        const float4* st_l = reinterpret_cast<const float4*>(sLse + (tile_cnt % kLseSlots) * 128 + grp * 64);
+        const float4* st_d = reinterpret_cast<const float4*>(sDelta + (tile_cnt % kDeltaSlots) * 128 + grp * 64);
         ++tile_cnt;
         // ---- phase 1: P^T = exp2(S^T*scale - lse[q]) -> bf16 -> Y
         PT_MARK(0)
@@ -980,12 +956,14 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           continue;
         }
         {
-          // observe the arrival of this tile's row statistics directly (they were copied on the dO
-          // stage's barrier); the phase cannot have advanced further: the stage is held until dV
-          const uint32_t pos = base + 2 * (uint32_t)i + 1;
+          // observe the arrival of this tile's lse row directly (it was copied on the Q stage's barrier,
+          // which has completed: S^T_i is done); the phase cannot have advanced further: the stage is held
+          // until dK_i
+          const uint32_t pos = base + 2 * (uint32_t)i;
           ok = mbar_wait(BAR(kRFull + pos % NS), (pos / NS) & 1, wctx, 523);
           if (!ok) break;
         }
+        PT_MARK(7)
         tc_fence_after();
         float pr[64];
         {
@@ -1003,8 +981,10 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           float x0, x1, x2, x3;
           unpack2(ffma2(pack2(pr[c4 * 4 + 0], pr[c4 * 4 + 1]), sc2, pack2(l.x, l.y)), x0, x1);
           unpack2(ffma2(pack2(pr[c4 * 4 + 2], pr[c4 * 4 + 3]), sc2, pack2(l.z, l.w)), x2, x3);
-          exp2_pair(2 * c4, x0, x1, pr[c4 * 4 + 0], pr[c4 * 4 + 1]);
-          exp2_pair(2 * c4 + 1, x2, x3, pr[c4 * 4 + 2], pr[c4 * 4 + 3]);
+          pr[c4 * 4 + 0] = ex2_approx(x0);
+          pr[c4 * 4 + 1] = ex2_approx(x1);
+          pr[c4 * 4 + 2] = ex2_approx(x2);
+          pr[c4 * 4 + 3] = ex2_approx(x3);
         }
         // masked KV token, or the phantom second half of an odd pair
         if (!kv_live || (BLK == 64 && grp == 1 && 2 * i + 1 >= entries)) {
@@ -1012,10 +992,12 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           for (int c = 0; c < 64; ++c) pr[c] = 0.f;
         }
         // Y still feeds dV / dK of the tile before until their commit
+        PT_MARK(2)
         if (y_cnt > 0) {
           ok = mbar_wait(BAR(kYFree), (y_cnt - 1) & 1, wctx, 524);
           if (!ok) break;
         }
+        PT_MARK(6)
         ++y_cnt;
         tc_fence_after();
         {
@@ -1030,6 +1012,12 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (!ok) break;
         PT_MARK(3)
         ++dp_cnt;
+        {
+          // the delta row came with the dO tile, which dP^T_i has read: the wait only makes the copy visible
+          const uint32_t pos = base + 2 * (uint32_t)i + 1;
+          ok = mbar_wait(BAR(kRFull + pos % NS), (pos / NS) & 1, wctx, 525);
+          if (!ok) break;
+        }
         tc_fence_after();
         uint32_t dp[64];
         tmem_ld32(tX + lane_base + grp * 64, dp);
@@ -1099,11 +1087,11 @@ using namespace bsa;
 
 #ifdef BSA_PHASE_TIMERS
 // development builds only: copies the backward phase counters to the host and clears them
-extern "C" int bsa_debug_read_bwd_prof(unsigned long long* host_out) {
+extern "C" int bsa_bwd_phase_timers(unsigned long long* host_out) {
   cudaDeviceSynchronize();
-  cudaMemcpyFromSymbol(host_out, g_bwd_prof, sizeof(unsigned long long) * 128);
+  cudaMemcpyFromSymbol(host_out, g_bwd_phase, sizeof(unsigned long long) * 128);
   static unsigned long long zeros[128];
-  cudaMemcpyToSymbol(g_bwd_prof, zeros, sizeof(zeros));
+  cudaMemcpyToSymbol(g_bwd_phase, zeros, sizeof(zeros));
   return 0;
 }
 #endif

@@ -3,7 +3,7 @@
 // One warp per query row (D = 128: one float4 per lane); pure HBM streaming, no shared memory.
 // Semantics of csrc/fwd/sm100_blk64/bsa_fwd_combine.py:253-566 (rows whose partial LSEs are all -inf
 // give zeros and lse = -inf, :458-468).
-#include "../../include/bsa_b200.h"
+#include "bsa_b200.h"
 #include "bsa_common.cuh"
 #include "bsa_host.h"
 

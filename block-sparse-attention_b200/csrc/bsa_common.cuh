@@ -110,9 +110,10 @@ struct WaitCtx {
 
 // Returns true when the phase with the given parity has completed, false when the CTA is aborting.
 // Must be called by all 32 lanes of a warp: the answer is made warp-uniform, so that warp-collective
-// instructions that follow are never executed by a partial warp.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx,
-                                          int site) {
+// instructions that follow are never executed by a partial warp.  `limit_ns` is the wall-clock budget of
+// this one wait (the kernels pass BSA_WAIT_LIMIT_NS; the self-test passes a short one and lets it expire).
+__device__ __forceinline__ bool mbar_wait_limit(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int site,
+                                                uint64_t limit_ns) {
   bool done = mbar_try_wait(bar, parity);
   if (!done) {
     const uint64_t t0 = globaltimer_ns();
@@ -123,7 +124,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
         break;
       }
       if (*ctx.abort_flag) break;
-      if (globaltimer_ns() - t0 > BSA_WAIT_LIMIT_NS) {
+      if (globaltimer_ns() - t0 > limit_ns) {
         *ctx.abort_flag = 1;
         if (atomicCAS(ctx.status, 0, (int)kStatusWaitTimeout) == 0) {
           ctx.status[1] = (int)blockIdx.x;
@@ -136,6 +137,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
     }
   }
   return __all_sync(0xffffffffu, done);
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int site) {
+  return mbar_wait_limit(bar, parity, ctx, site, BSA_WAIT_LIMIT_NS);
 }
 
 // Non-blocking test of a phase (mbarrier.test_wait never suspends the thread).
@@ -498,6 +502,19 @@ __device__ __forceinline__ void unpack_f16x2(uint32_t h2, float& lo, float& hi) 
       : "r"(h2));
 }
 
+__device__ __forceinline__ uint32_t hadd2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("add.rn.f16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+// two packed pairs of halves -> packed e4m3x4, the low half of `lo` in bits [0,8)
+__device__ __forceinline__ uint32_t pack_e4m3x4_f16(uint32_t lo, uint32_t hi) {
+  uint16_t l, h;
+  asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(l) : "r"(lo));
+  asm("cvt.rn.satfinite.e4m3x2.f16x2 %0, %1;" : "=h"(h) : "r"(hi));
+  return (uint32_t)l | ((uint32_t)h << 16);
+}
+
 // three-input maximum (one instruction on sm_100)
 __device__ __forceinline__ float fmax3(float a, float b, float c) {
   float d;
@@ -528,33 +545,6 @@ __device__ __forceinline__ uint64_t fmul2(uint64_t a, uint64_t b) {
   asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
   return d;
 }
-// 2^x for a packed pair on the FMA pipe instead of the special-function unit: x is clamped to >= -127,
-// split into floor and fraction with the 2^23+2^22 round-down trick, the fraction goes through a
-// degree-3 polynomial (max relative error 8.8e-5, far below the bf16 rounding of the result) and the
-// integer part is added into the exponent field.
-__device__ __forceinline__ uint64_t ex2_emu2(float x0, float x1) {
-  x0 = fmaxf(x0, -127.f);
-  x1 = fmaxf(x1, -127.f);
-  const uint64_t x = pack2(x0, x1);
-  const uint64_t magic = pack2(12582912.f, 12582912.f);
-  uint64_t t;
-  asm("add.rm.ftz.f32x2 %0, %1, %2;" : "=l"(t) : "l"(x), "l"(magic));
-  uint64_t r;
-  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(t), "l"(magic));
-  uint64_t f;
-  asm("sub.rn.f32x2 %0, %1, %2;" : "=l"(f) : "l"(x), "l"(r));
-  uint64_t pl = ffma2(f, pack2(0.077119089663028717041015625f, 0.077119089663028717041015625f),
-                      pack2(0.227564394474029541015625f, 0.227564394474029541015625f));
-  pl = ffma2(pl, f, pack2(0.695146143436431884765625f, 0.695146143436431884765625f));
-  pl = ffma2(pl, f, pack2(1.f, 1.f));
-  float t0, t1, p0, p1;
-  unpack2(t, t0, t1);
-  unpack2(pl, p0, p1);
-  const uint32_t r0 = __float_as_uint(p0) + (__float_as_uint(t0) << 23);
-  const uint32_t r1 = __float_as_uint(p1) + (__float_as_uint(t1) << 23);
-  return pack2(__uint_as_float(r0), __uint_as_float(r1));
-}
-
 // register re-partitioning between warpgroups (every warp of the warpgroup must execute it)
 template <int N>
 __device__ __forceinline__ void setmaxnreg_inc() {

@@ -2,12 +2,11 @@
 // tcgen05 QK^T and PV MMAs accumulating in tensor memory, online softmax with LSE.
 //
 // One persistent CTA per SM walks (q tile, split) work items.  Warp roles:
-//   warps 0-3  softmax group 0: owns stream 0 (KV iterations 0, 2, 4, ...), one thread per query row
-//   warps 4-7  softmax group 1: owns stream 1 (KV iterations 1, 3, 5, ...)
-//   warps 8-9  MMA issue, one warp (one lane) per stream
-//   warp  10   TMA producer (one lane)
-//   warp  11   idle: it completes the third warpgroup so that registers can be re-partitioned
-//              (setmaxnreg) in favour of the softmax groups
+//   warps 0-3   softmax group 0: owns stream 0 (KV iterations 0, 2, 4, ...), one thread per query row
+//   warps 4-7   softmax group 1: owns stream 1 (KV iterations 1, 3, 5, ...)
+//   warps 8-9   MMA issue, one warp (one lane) per stream
+//   warps 10-11 TMA producers, one warp (one lane) per stream; producer 0 also loads the Q tiles
+// The four non-softmax warps give registers up (setmaxnreg) in favour of the softmax groups.
 // Tensor memory (512 columns): S0 @0, S1 @128, O0 @256, O1 @384 (fp32, 128 lanes x 128 columns each);
 // the probabilities P_s overwrite the head of S_s (bf16: 64 columns, e4m3: 32 columns) and are the
 // A operand of the PV MMA straight from tensor memory.  The two streams keep independent running
@@ -21,25 +20,18 @@
 // softmax rules csrc/utils/softmax.py:102-192, merge and LSE :1551-1636) and
 // csrc/fwd/sm100_blk64/bsa_fwd_sm100.py; the Sage FP8 scale handling follows
 // csrc/fwd/sm100_blk128/bsa_fwd_sm100_fp8_fused_pv.py:1510-1663.
-#include "../../include/bsa_b200.h"
+#include "bsa_b200.h"
 #include "bsa_common.cuh"
 #include "bsa_host.h"
 
 #include <type_traits>
 
-// Phase timers (development aid, see bsa_common.cuh): the 64-slot buffer of an unsplit launch travels in
-// the otherwise unused partial_lse pointer.
-#define PT_FLUSH(base) PT_FLUSH_TO(reinterpret_cast<unsigned long long*>(p.partial_lse), base)
-#ifdef BSA_PHASE_TRACE
-// development aid: CTA 0 records clock64() of selected events of its first iterations behind the 64 counters
-#define PT_TRACE(stream, slot) if (blockIdx.x == 0 && (threadIdx.x & 31) == 0 && pt_trace_n[stream] < 256) { \
-    reinterpret_cast<unsigned long long*>(p.partial_lse)[64 + (stream) * 1024 + pt_trace_n[stream] * 4 + (slot)] = clock64(); }
-#define PT_TRACE_NEXT(stream) ++pt_trace_n[stream];
-#define PT_TRACE_DECL int pt_trace_n[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#ifdef BSA_PHASE_TIMERS
+// Development builds only (build.py --phase-timers): per-role clock counters, read by bsa_fwd_phase_timers().
+__device__ unsigned long long g_fwd_phase[64];
+#define PT_FLUSH(base) PT_FLUSH_TO(g_fwd_phase, base)
 #else
-#define PT_TRACE(stream, slot)
-#define PT_TRACE_NEXT(stream)
-#define PT_TRACE_DECL
+#define PT_FLUSH(base)
 #endif
 
 namespace bsa {
@@ -66,17 +58,6 @@ struct FwdParams {
   int num_work;  // B * Hidx * NqT * splits
   float scale_log2;
 };
-
-// Of every eight column pairs of a softmax row, this many take the polynomial exp2 on the FMA pipe
-// instead of the special-function unit.  Measured on B200 (cfg2 forward): 0 -> 3.73 ms, 1 -> 3.87 ms,
-// 2 -> 3.97 ms, 4 -> 4.30 ms: the kernel is bound by its dependency chain, not by the SFU, so it is off.
-#ifndef BSA_EX2_EMU8
-#define BSA_EX2_EMU8 0
-#endif
-// Same idea for the e4m3 path, counted in pairs out of four.
-#ifndef BSA_EX2_EMU_FP8
-#define BSA_EX2_EMU_FP8 0
-#endif
 
 constexpr int kThreads = 384;
 constexpr int kSoftmaxThreads = 256;
@@ -359,7 +340,6 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint64_t k_desc0 = umma_desc_sw128(smem_u32(sKV), 0, 1024);                               // K-major view
     const uint64_t v_desc0 = umma_desc_sw128(smem_u32(sKV), FP8 ? 0u : (uint32_t)Cfg::kSlabBytes, 1024);  // MN-major
     PT_DECL
-    PT_TRACE_DECL
     for (int band = 0; band * (int)gridDim.x < p.num_work && ok; ++band) {
       const int w = snake_work(band);
       if (w >= p.num_work) continue;
@@ -380,7 +360,6 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         PT_MARK(2)
         if (take_turn && !turn_wait()) return false;
         PT_MARK(5)
-        PT_TRACE(4 + s, 0)
         PT_MARK(0)
         {
           const uint32_t led = lane == 0;
@@ -395,8 +374,6 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           umma_commit_led(BAR(kKvEmpty + stage), led);
         }
         PT_MARK(7)
-        PT_TRACE(4 + s, 2)
-        PT_TRACE_NEXT(4 + s)
         return true;
       };
       auto issue_pv = [&](int i, bool take_turn) -> bool {
@@ -409,7 +386,6 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         PT_MARK(4)
         if (take_turn && !turn_wait()) return false;
         PT_MARK(5)
-        PT_TRACE(2 + s, 0)
         tc_fence_after();
         const uint64_t vd = v_desc0 + (uint64_t)stage * (Cfg::kTileBytes >> 4);
         auto pv_steps = [&](int k0, int k1) {
@@ -421,14 +397,11 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             const uint32_t a_t = tS_s + (uint32_t)k * Cfg::kPColsPerStep;
             if (FP8) umma_f8_ts_led(tO_s, a_t, db, idesc_pv, (i >= 2) || (k > 0), lane == 0);
             else umma_f16_ts_led(tO_s, a_t, db, idesc_pv, (i >= 2) || (k > 0), lane == 0);
-            if (k < 4) { PT_TRACE(6 + s, k & 3) }
           }
         };
         PT_MARK(0)
         pv_steps(0, Cfg::kKSteps / 2);
         PT_MARK(6)
-        PT_TRACE(2 + s, 3)
-        PT_TRACE_NEXT(6 + s)
         PT_MARK(0)
         if (!mbar_wait(BAR(kPFull + s), p_cnt & 1, wctx, 204)) return false;  // second half
         PT_MARK(4)
@@ -457,11 +430,8 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
       for (int i = s; i < n_it && ok; i += 2) {
         ok = issue_pv(i, turns);
-        PT_TRACE(2 + s, 1)
         if (ok && i + 2 < n_it) ok = issue_qk(i + 2, false);
         if (ok && turns && i + 1 < n_it) turn_pass();
-        PT_TRACE(2 + s, 2)
-        PT_TRACE_NEXT(2 + s)
       }
       if (!ok) break;
       // Q is free once the QK MMAs of BOTH streams have completed: each issuer signals for its own MMAs
@@ -493,7 +463,6 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     constexpr float kRescaleThreshold = FP8 ? 1.8073549f /* log2(448/128) */ : 8.0f;
     constexpr float kPBias = FP8 ? 7.0f : 0.0f;
     PT_DECL
-    PT_TRACE_DECL
 
     for (int band = 0; band * (int)gridDim.x < p.num_work && ok; ++band) {
       const int w = snake_work(band);
@@ -556,7 +525,6 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         ok = mbar_wait(BAR(kSFull + grp), s_cnt & 1, wctx, 300 + grp);
         if (!ok) break;
         PT_MARK(1)
-        if ((warp & 3) == 0) { PT_TRACE(grp, 0) }
         ++s_cnt;
         tc_fence_after();
         if (!row_active) {
@@ -689,61 +657,74 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         const float m_used = (m_cur == -INFINITY) ? 0.f : m_cur;
         const float neg_m = kPBias - m_used;
         PT_MARK(3)
-        if ((warp & 3) == 0) { PT_TRACE(grp, 1) }
         // ---- exponentials, row sum, P to tensor memory
         float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
         if (FP8) {
           const uint64_t nm2 = pack2(neg_m, neg_m);
-          uint64_t s0 = pack2(0.f, 0.f), s1 = s0;
+          if (masked) {
+            // rare path (tail or shortened block): fp32 exponentials; masked columns hold -inf and a zero
+            // scale there would make NaN, so they are selected explicitly
 #pragma unroll
-          for (int c4 = 0; c4 < 4; ++c4) {
-            uint32_t pk[8];
+            for (int c4 = 0; c4 < 4; ++c4) {
+              uint32_t pk[8];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              const int c = c4 * 32 + e * 4;
-              const float sc = ksc[c >> 4];
-              float x0, x1, x2, x3;
-              if (masked) {
-                // masked columns hold -inf; a zero scale there would make NaN, so select explicitly
-                x0 = (sv[c] == -INFINITY) ? 0.f : ex2_approx(fmaf(sv[c], sc, neg_m));
-                x1 = (sv[c + 1] == -INFINITY) ? 0.f : ex2_approx(fmaf(sv[c + 1], sc, neg_m));
-                x2 = (sv[c + 2] == -INFINITY) ? 0.f : ex2_approx(fmaf(sv[c + 2], sc, neg_m));
-                x3 = (sv[c + 3] == -INFINITY) ? 0.f : ex2_approx(fmaf(sv[c + 3], sc, neg_m));
-              } else {
+              for (int e = 0; e < 8; ++e) {
+                const int c = c4 * 32 + e * 4;
+                const float sc = ksc[c >> 4];
+                const float x0 = (sv[c] == -INFINITY) ? 0.f : ex2_approx(fmaf(sv[c], sc, neg_m));
+                const float x1 = (sv[c + 1] == -INFINITY) ? 0.f : ex2_approx(fmaf(sv[c + 1], sc, neg_m));
+                const float x2 = (sv[c + 2] == -INFINITY) ? 0.f : ex2_approx(fmaf(sv[c + 2], sc, neg_m));
+                const float x3 = (sv[c + 3] == -INFINITY) ? 0.f : ex2_approx(fmaf(sv[c + 3], sc, neg_m));
+                a0 += x0; a1 += x1; a2 += x2; a3 += x3;
+                pk[e] = pack_e4m3x4(x0, x1, x2, x3);
+              }
+              if (c4 == 2) {
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(BAR(kPHalf + grp));
+              }
+              tmem_st8(tS[grp] + lane_base + c4 * 8, pk);
+            }
+          } else {
+            // The probabilities are rounded to e4m3 (three mantissa bits), so the exponentials are taken in
+            // packed half precision: two results per special-function operation, one conversion to e4m3 per
+            // pair.  The row sum runs in packed halves over at most 32 columns (four partial sums of four
+            // terms, <= 4 * 448) and is flushed to fp32 per chunk.
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+              uint32_t pk[8];
+              uint32_t hs[4];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const int c = c4 * 32 + e * 4;
+                const float sc = ksc[c >> 4];
                 const uint64_t sc2 = pack2(sc, sc);
+                float x0, x1, x2, x3;
                 unpack2(ffma2(pack2(sv[c], sv[c + 1]), sc2, nm2), x0, x1);
                 unpack2(ffma2(pack2(sv[c + 2], sv[c + 3]), sc2, nm2), x2, x3);
-                // e4m3 packing shares the special-function pipe with ex2, which bounds this loop: a share of
-                // the exponentials takes the polynomial on the FMA pipe instead
-                if (((2 * e) & 3) < BSA_EX2_EMU_FP8) {
-                  unpack2(ex2_emu2(x0, x1), x0, x1);
+                const uint32_t e01 = ex2_f16x2(pack_f16x2(x0, x1));
+                const uint32_t e23 = ex2_f16x2(pack_f16x2(x2, x3));
+                if (e < 2) {
+                  hs[2 * e] = e01;
+                  hs[2 * e + 1] = e23;
                 } else {
-                  x0 = ex2_approx(x0);
-                  x1 = ex2_approx(x1);
+                  hs[(2 * e) & 3] = hadd2(hs[(2 * e) & 3], e01);
+                  hs[(2 * e + 1) & 3] = hadd2(hs[(2 * e + 1) & 3], e23);
                 }
-                if (((2 * e + 1) & 3) < BSA_EX2_EMU_FP8) {
-                  unpack2(ex2_emu2(x2, x3), x2, x3);
-                } else {
-                  x2 = ex2_approx(x2);
-                  x3 = ex2_approx(x3);
-                }
+                pk[e] = pack_e4m3x4_f16(e01, e23);
               }
-              s0 = fadd2(s0, pack2(x0, x1));
-              s1 = fadd2(s1, pack2(x2, x3));
-              pk[e] = pack_e4m3x4(x0, x1, x2, x3);
+              float lo, hi;
+              unpack_f16x2(hadd2(hadd2(hs[0], hs[1]), hadd2(hs[2], hs[3])), lo, hi);
+              if (c4 & 1) { a2 += lo; a3 += hi; } else { a0 += lo; a1 += hi; }
+              if (c4 == 2) {
+                // first half of P_s (two MMA k steps) released on its own barrier, its stores long landed
+                tmem_wait_st();
+                tc_fence_before();
+                mbar_arrive(BAR(kPHalf + grp));
+              }
+              tmem_st8(tS[grp] + lane_base + c4 * 8, pk);
             }
-            if (c4 == 2) {
-              // first half of P_s (two MMA k steps) released on its own barrier, its stores long landed
-              tmem_wait_st();
-              tc_fence_before();
-              mbar_arrive(BAR(kPHalf + grp));
-            }
-            tmem_st8(tS[grp] + lane_base + c4 * 8, pk);
           }
-          float y0, y1, y2, y3;
-          unpack2(s0, y0, y1);
-          unpack2(s1, y2, y3);
-          a0 = y0; a1 = y1; a2 = y2; a3 = y3;
         } else {
           // the loop is instantiated once per 16-bit format so that the choice costs nothing per element
           auto exp_store = [&](auto is_f16) {
@@ -758,17 +739,10 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               const int c = c4 * 32 + e * 2;
               float x0, x1;
               unpack2(ffma2(pack2(sv[c], sv[c + 1]), sc2, nm2), x0, x1);
-              uint64_t pe;
-              if ((e & 7) < BSA_EX2_EMU8) {
-                pe = ex2_emu2(x0, x1);
-                unpack2(pe, x0, x1);
-              } else {
-                x0 = ex2_approx(x0);
-                x1 = ex2_approx(x1);
-                pe = pack2(x0, x1);
-              }
-              if (e & 1) s1 = fadd2(s1, pe);
-              else s0 = fadd2(s0, pe);
+              x0 = ex2_approx(x0);
+              x1 = ex2_approx(x1);
+              if (e & 1) s1 = fadd2(s1, pack2(x0, x1));
+              else s0 = fadd2(s0, pack2(x0, x1));
               pk[e] = decltype(is_f16)::value ? pack_f16x2(x0, x1) : pack_bf16x2(x0, x1);
             }
             if (c4 == 2) {
@@ -790,12 +764,10 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
         l_sum += (a0 + a1) + (a2 + a3);
         PT_MARK(4)
-        if ((warp & 3) == 0) { PT_TRACE(grp, 2) }
         tmem_wait_st();
         tc_fence_before();
         mbar_arrive(BAR(kPFull + grp));
         PT_MARK(5)
-        if ((warp & 3) == 0) { PT_TRACE(grp, 3) PT_TRACE_NEXT(grp) }
       }
       if (!ok) break;
 
@@ -908,8 +880,8 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           p.lse[((long long)t.b * p.Hq + hq) * p.Sq + seq] = lse_log2 * kLn2;
         }
       }
+      PT_MARK(7)
     }
-    PT_MARK(7)
     if ((threadIdx.x & 127) == 0 && !SPLIT) tma_store_wait_all<0>();
     if ((warp & 3) == 0) { PT_FLUSH(grp * 8) }
   } else {
@@ -952,6 +924,17 @@ static int launch_fwd(const bsa_fwd_args& a, const FwdParams& p, const CUtensorM
 }  // namespace bsa
 
 using namespace bsa;
+
+#ifdef BSA_PHASE_TIMERS
+// development builds only: copies the forward phase counters to the host and clears them
+extern "C" int bsa_fwd_phase_timers(unsigned long long* host_out) {
+  cudaDeviceSynchronize();
+  cudaMemcpyFromSymbol(host_out, g_fwd_phase, sizeof(unsigned long long) * 64);
+  static unsigned long long zeros[64];
+  cudaMemcpyToSymbol(g_fwd_phase, zeros, sizeof(zeros));
+  return 0;
+}
+#endif
 
 extern "C" int bsa_fwd(const bsa_fwd_args* a, void* cuda_stream) {
   if (!a) return set_error(BSA_ERR_INVALID, "bsa_fwd: null args");

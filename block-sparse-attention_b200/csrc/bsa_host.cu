@@ -5,9 +5,28 @@
 #include <stdio.h>
 #include <string.h>
 
-#include "../../include/bsa_b200.h"
+#include "bsa_b200.h"
+#include "bsa_common.cuh"
 
 namespace bsa {
+
+// Self-test of the bounded wait: two warps wait on an mbarrier that nobody ever arrives at.  The first thread
+// whose budget runs out records the status word and raises the abort flag, the other warp leaves through the
+// flag, and both fall through to the end of the kernel - the same path every role of the tcgen05 kernels takes.
+__global__ void __launch_bounds__(64, 1) selftest_wait_kernel(int* status, int* returned, unsigned long long limit_ns) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    abort_flag = 0;
+    mbar_init(smem_u32(&bar), 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  WaitCtx ctx{&abort_flag, status};
+  const bool ok = mbar_wait_limit(smem_u32(&bar), 0, ctx, 900 + (int)(threadIdx.x >> 5), limit_ns);
+  __syncthreads();  // the common teardown point
+  if (threadIdx.x == 0) *returned = ok ? 2 : 1;
+}
 
 static thread_local char g_error[512] = "";
 
@@ -69,6 +88,16 @@ int make_tensor_map(CUtensorMap* map, CUtensorMapDataType dtype, int rank, const
 extern "C" int bsa_abi_version(void) { return BSA_B200_ABI_VERSION; }
 
 extern "C" const char* bsa_last_error(void) { return bsa::g_error; }
+
+extern "C" int bsa_selftest_wait(uint64_t limit_ns, int32_t* status, int32_t* returned, void* cuda_stream) {
+  if (!status || !returned) return bsa::set_error(BSA_ERR_INVALID, "bsa_selftest_wait: null pointer");
+  if (limit_ns == 0 || limit_ns > 1000000000ull)
+    return bsa::set_error(BSA_ERR_INVALID, "bsa_selftest_wait: limit must be in (0, 1 s]");
+  bsa::selftest_wait_kernel<<<1, 64, 0, reinterpret_cast<cudaStream_t>(cuda_stream)>>>(status, returned, limit_ns);
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return bsa::set_error(BSA_ERR_CUDA, "selftest launch: %s", cudaGetErrorString(e));
+  return BSA_OK;
+}
 
 extern "C" int bsa_num_sms(int device) {
   static int cached[64];

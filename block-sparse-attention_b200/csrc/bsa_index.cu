@@ -6,7 +6,7 @@
 // csrc/bwd/bucketed_k2q_csr.py:114-238 and its CPU model tests/test_bucketed_k2q_csr.py:12-74
 // (one edge per occurrence, ids outside [0,Nkv) dropped, counts clamped to [0,cap], offsets running
 // across the query groups of one (batch, head)).
-#include "../../include/bsa_b200.h"
+#include "bsa_b200.h"
 #include "bsa_common.cuh"
 #include "bsa_host.h"
 
@@ -189,14 +189,20 @@ csr_unshift_kernel(int32_t* __restrict__ offsets, int G, int Nkv) {
   }
 }
 
-constexpr int kSortSmemInts = 1024;
+constexpr int kSortSmemInts = 1024;       // per warp: 1024 entries of a short row, or 4096 byte counters
+constexpr int kSortCountRange = 4 * kSortSmemInts;
+constexpr int kSortRankMax = 64;          // rows up to this length are rank-sorted (n^2 / 32 steps per lane)
 
-// one warp per CSR row: ascending order.  Rows of up to 1024 entries are rank-sorted through shared
-// memory; longer rows (only possible with buckets above 1024 q-blocks) use an in-place odd-even
-// transposition sort in global memory.
+// One warp per CSR row: ascending order, in place.  Every entry of a row of query group g is a query block of
+// that group, i.e. lies in [g * bucket, g * bucket + bucket): rows longer than kSortRankMax are therefore
+// sorted by counting (one byte counter per query block of the group in shared memory, O(n + bucket) work, any
+// row length) as long as the group has at most kSortCountRange query blocks - which covers every default
+// bucket (384 / 512 / 1088 / 1152).  Short rows are rank-sorted.  What is left (a caller-chosen bucket above
+// 4096 blocks, or a query block listed more than 255 times in one row) takes a rank sort up to 1024 entries
+// and an odd-even transposition sort in global memory beyond.
 __global__ void __launch_bounds__(128)
 csr_sort_kernel(const int32_t* __restrict__ offsets, int32_t* __restrict__ indices, long long n_rows,
-                int G, int Nkv, long long idx_cap) {
+                int G, int Nkv, int Nq, int bucket, long long idx_cap) {
   __shared__ int32_t buf[4][kSortSmemInts];
   const long long r = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
   if (r >= n_rows) return;
@@ -206,11 +212,62 @@ csr_sort_kernel(const int32_t* __restrict__ offsets, int32_t* __restrict__ indic
   const int kv = (int)(r % Nkv);
   const long long bhg = r / Nkv;
   const long long bh = bhg / G;
+  const int g = (int)(bhg % G);
   const int32_t* off = offsets + bhg * (long long)(Nkv + 1);
   const int beg = off[kv], end = off[kv + 1];
   const int n = end - beg;
   if (n <= 1) return;
   int32_t* row = indices + bh * idx_cap + beg;
+  const int q_lo = g * bucket;
+  const int range = min(bucket, Nq - q_lo);
+  bool counted = false;
+  if (n > kSortRankMax && range <= kSortCountRange) {
+    uint32_t* cnt = reinterpret_cast<uint32_t*>(buf[w]);
+    const int words = (range + 3) >> 2;
+    for (int i = lane; i < words; i += 32) cnt[i] = 0;
+    __syncwarp();
+    bool overflow = false;
+    for (int i = lane; i < n; i += 32) {
+      const int q = row[i] - q_lo;
+      if (q < 0 || q >= range) {  // cannot happen for rows written by the scatter pass; never index outside
+        overflow = true;
+        continue;
+      }
+      const uint32_t sh = 8u * (uint32_t)(q & 3);
+      const uint32_t old = atomicAdd(cnt + (q >> 2), 1u << sh);
+      overflow |= ((old >> sh) & 0xffu) == 0xffu;
+    }
+    overflow = __any_sync(0xffffffffu, overflow);
+    __syncwarp();
+    if (!overflow) {
+      // lane l owns the counters of words [l * wpl, (l + 1) * wpl): its share of the output starts at the
+      // exclusive prefix of the lanes below
+      const int wpl = (words + 31) >> 5;
+      const int w0 = lane * wpl, w1 = min(words, w0 + wpl);
+      int mine = 0;
+      for (int j = w0; j < w1; ++j) {
+        const uint32_t c = cnt[j];
+        mine += (int)((c & 0xffu) + ((c >> 8) & 0xffu) + ((c >> 16) & 0xffu) + (c >> 24));
+      }
+      int incl = mine;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += y;
+      }
+      int pos = incl - mine;
+      for (int j = w0; j < w1; ++j) {
+        uint32_t c = cnt[j];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          for (int k = (int)(c & 0xffu); k > 0; --k) row[pos++] = q_lo + 4 * j + b;
+          c >>= 8;
+        }
+      }
+      counted = true;
+    }
+  }
+  if (counted) return;
   if (n <= kSortSmemInts) {
     for (int i = lane; i < n; i += 32) buf[w][i] = row[i];
     __syncwarp();
@@ -380,7 +437,8 @@ extern "C" int bsa_build_k2q_csr(const int32_t* q2k_index, const int32_t* q2k_nu
     csr_unshift_kernel<<<(unsigned)((long long)B * H * G), 256, 0, st>>>(offsets, G, Nkv);
     if ((rc = check_launch("csr_unshift"))) return rc;
     const long long n_rows = (long long)B * H * G * Nkv;
-    csr_sort_kernel<<<(unsigned)((n_rows + 3) / 4), 128, 0, st>>>(offsets, indices, n_rows, G, Nkv, idx_cap);
+    csr_sort_kernel<<<(unsigned)((n_rows + 3) / 4), 128, 0, st>>>(offsets, indices, n_rows, G, Nkv, Nq,
+                                                                   bucket_size_blocks, idx_cap);
     if ((rc = check_launch("csr_sort"))) return rc;
   }
   return BSA_OK;

@@ -6,7 +6,7 @@
 //   V: per (head, c)   scale = max(max_{b,s} |v|, 1e-3) / 448, value = e4m3(v * (1 / scale))
 // Recipe of bsa_fp8_quant.py:10-104 (the Triton kernels behind quantize_sage_bhsd), pinned by
 // tests/test_bsa_fp8_quant.py:34-63.
-#include "../../include/bsa_b200.h"
+#include "bsa_b200.h"
 #include "bsa_common.cuh"
 #include "bsa_host.h"
 

@@ -7,7 +7,7 @@
 //   block_mean:   x [B,H,S,D] bf16 -> per-block mean [B,H,N,D] fp32      (reads x once)
 //   pooled_score: qm [.,Nq,D], km [.,Nkv,D] -> scores [.,Nq,Nkv] fp32    (fixed summation order)
 //   topk_rows:    scores [rows,Nkv] -> index [rows,cap], first k entries (bitonic sorts in shared memory)
-#include "../../include/bsa_b200.h"
+#include "bsa_b200.h"
 #include "bsa_common.cuh"
 #include "bsa_host.h"
 

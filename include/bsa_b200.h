@@ -40,6 +40,15 @@ int bsa_abi_version(void);
 const char* bsa_last_error(void);
 /* Number of SMs of `device` (148 on B200); the persistent grids are sized from it. */
 int bsa_num_sms(int device);
+/*
+ * Self-test of the bounded device-side wait (no counterpart in the reference, whose waits are unbounded:
+ * csrc/fwd/sm100_blk64/bsa_fwd_helpers.py:41-86).  Launches one small CTA whose two warps wait, with a
+ * budget of `limit_ns` nanoseconds (at most 1 s), on an mbarrier that nothing arrives at - the same wait
+ * routine every role of the attention kernels uses.  When the budget runs out the kernel writes
+ * status[0..3] = {1, block, site 900 or 901, thread}, leaves through the common exit and sets *returned = 1.
+ * Nothing faults and the context stays usable; `status` is int32[4], zeroed by the caller, `returned` int32[1].
+ */
+int bsa_selftest_wait(uint64_t limit_ns, int32_t* status, int32_t* returned, void* cuda_stream);
 
 /*
  * Forward attention over the KV blocks selected by q2k_block_index.

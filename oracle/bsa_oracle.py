@@ -245,11 +245,14 @@ def backward_dense(q, k, v, dout, attn_bias, softmax_scale, upcast=True):
 
 
 def backward_gathered(q, k, v, dout, index, count, nums=None, scale=None, blk=128, heads=None, batches=None,
-                      sizes=None):
+                      sizes=None, upcast=True):
     """Gathered-form backward for large shapes (MHA): per query block, autograd through the softmax over
     exactly the selected tokens; gradients scattered back.  Same math as ``backward_dense`` (the dense
     bias only removes the unselected tokens), so it is validated against it on small cases.  ``sizes``
-    (rank 1/2/3) are the valid-token counts of the KV blocks, as in ``attention_gathered``."""
+    (rank 1/2/3) are the valid-token counts of the KV blocks, as in ``attention_gathered``.  ``upcast=False``
+    keeps the tile arithmetic in the inputs' own dtype (the "PyTorch implementation in bf16" whose distance
+    from the fp32 result sets the reference's tolerance, tests/test_flash_bwd.py:53-61)."""
+    cdt = torch.float32 if upcast else q.dtype
     B, H, Sq, D = q.shape
     Sk = k.shape[2]
     scale = D ** -0.5 if scale is None else scale
@@ -259,7 +262,7 @@ def backward_gathered(q, k, v, dout, index, count, nums=None, scale=None, blk=12
     off = torch.arange(blk)
     for b in (range(B) if batches is None else batches):
         for h in (range(H) if heads is None else heads):
-            kf, vf = k[b, h].float(), v[b, h].float()
+            kf, vf = k[b, h].to(cdt), v[b, h].to(cdt)
             for m in range(index.shape[2]):
                 n = count if nums is None else int(nums[b, h, m])
                 n = max(0, min(n, index.shape[-1]))
@@ -275,16 +278,16 @@ def backward_gathered(q, k, v, dout, index, count, nums=None, scale=None, blk=12
                 toks = toks[toks < Sk]
                 if toks.numel() == 0:
                     continue
-                qt = q[b, h, s:e].float()
+                qt = q[b, h, s:e].to(cdt)
                 kt, vt = kf[toks], vf[toks]
-                do = dout[b, h, s:e].float()
+                do = dout[b, h, s:e].to(cdt)
                 p = torch.softmax((qt @ kt.T) * scale, dim=-1)
                 dp = do @ vt.T
                 delta = (p * dp).sum(-1, keepdim=True)
                 ds = p * (dp - delta)
-                dq[b, h, s:e] = (ds @ kt) * scale
-                dk[b, h].index_add_(0, toks, (ds.T @ qt) * scale)
-                dv[b, h].index_add_(0, toks, p.T @ do)
+                dq[b, h, s:e] = ((ds @ kt) * scale).float()
+                dk[b, h].index_add_(0, toks, ((ds.T @ qt) * scale).float())
+                dv[b, h].index_add_(0, toks, (p.T @ do).float())
     return dq, dk, dv
 
 
@@ -442,6 +445,23 @@ def blk64_auto_kv_splits(batch, heads, seqlen_q, kv_blocks, max_kv_splits: int =
     if batch * heads * ceil_div(seqlen_q, 64) >= 512:
         return 1
     return blk64_kv_splits_from_count(kv_blocks, max_kv_splits)
+
+
+def blk64_auto_fp8_kv_splits(kv_blocks: int, heads: int, seqlen_q: int, batch: int, num_sms: int) -> int:
+    """bsa_attn_interface.py:693-718: no split when the 64-row query tiles fill the SMs; otherwise the largest
+    power of two <= 16 whose (tile, split) items still fit the SMs, reduced until each split keeps >= 8 blocks
+    and a two-way split >= 128 blocks in total."""
+    tiles = batch * heads * ceil_div(seqlen_q, 64)
+    if tiles >= num_sms:
+        return 1
+    best = 1
+    for s in (2, 4, 8, 16):
+        if s * tiles <= num_sms:
+            best = s
+    for s in (16, 8, 4, 2):
+        if s <= best and kv_blocks >= 8 * s and (s != 2 or kv_blocks >= 128):
+            return s
+    return 1
 
 
 # --------------------------------------------------------------------------------------------------

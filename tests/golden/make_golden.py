@@ -35,7 +35,7 @@ def rand_bf16(gen, *shape, scale=1.0):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the reference checkout")
     args = ap.parse_args()
     ref = os.path.abspath(args.reference)
     sys.path.insert(0, os.path.join(ref, "tests"))
@@ -219,6 +219,16 @@ def main():
     counts = [1, 2, 31, 255, 256, 449, 450, 899, 900, 2048]
     table = [ref_iface._sm100_blk64_kv_splits_from_count(c) for c in counts]
     np.savez_compressed(os.path.join(HERE, "policy_blk64_splits.npz"), counts=np.array(counts), splits=np.array(table))
+    # the automatic split policy of the Sage FP8 64-token forward over a grid of (kv_blocks, heads, seqlen_q,
+    # batch, num_sms) that contains every row of the table in the reference's tests/test_bsa_fp8_fwd.py:17-66
+    rows = []
+    for heads, seqlen_q in ((4, 64), (8, 64), (1, 64 * 37), (1, 64 * 74), (1, 64 * 100), (1, 64 * 148), (4, 119040),
+                            (8, 349440), (4, 579840), (8, 695040), (4, 49290 + 2216 + 752), (2, 640), (3, 1000)):
+        for kv_blocks in (1, 7, 8, 15, 16, 31, 32, 63, 64, 127, 128, 188, 255, 256, 548, 909, 915, 1089, 2048):
+            for batch, num_sms in ((1, 148), (8, 148), (37, 148), (1, 200), (2, 132)):
+                rows.append((kv_blocks, heads, seqlen_q, batch, num_sms,
+                             ref_iface._sm100_blk64_auto_fp8_kv_splits(kv_blocks, heads, seqlen_q, batch, num_sms)))
+    np.savez_compressed(os.path.join(HERE, "policy_fp8_blk64_splits.npz"), rows=np.array(rows, dtype=np.int64))
     print("golden vectors written to", HERE)
 
 

@@ -1,4 +1,4 @@
-"""GPU: the BASELINE configurations 3, 4 and 5 at their full sizes.  The CUDA path is compared with the CPU
+"""GPU: the BASELINE configurations 2, 3, 4 and 5 at their full sizes.  The CUDA path is compared with the CPU
 oracle on a sample of (head, query tile) slices (the oracle needs seconds per slice at these sizes) and
 through size-independent properties on the whole output: empty rows are exact zeros with LSE = -inf,
 repeated calls are bit-identical, split-KV agrees with the unsplit run."""
@@ -16,6 +16,69 @@ pytestmark = pytest.mark.gpu
 def _randn_bf16(shape, seed):
     g = torch.Generator(device="cuda").manual_seed(seed)
     return torch.randn(shape, generator=g, device="cuda").to(torch.bfloat16)
+
+
+def _uniform_index(B, H, Nq, Nkv, count, seed):
+    """diagonal + (count - 1) distinct uniform others per row, ascending int32 (BASELINE config 2's rule)."""
+    g = torch.Generator().manual_seed(seed)
+    keys = torch.rand(B, H, Nq, Nkv, generator=g)
+    keys[..., torch.arange(Nq), torch.arange(Nq).clamp(max=Nkv - 1)] = -1.0
+    return keys.argsort(dim=-1)[..., :count].sort(dim=-1).values.to(torch.int32).contiguous()
+
+
+def _check_fwd_bwd_slices(q, k, v, do, index, count, got, slices, blk=128):
+    """O / LSE against the gathered fp32 oracle within 3e-2 / 2e-3 (tests/test_flash_fwd.py:573-585) and the
+    gradients within 3 * |bf16 - fp32| + 3 * bf16 eps + 5e-3 (tests/test_flash_bwd.py:53-61) on (batch, head)
+    slices."""
+    from helpers import bf16_roundtrip_eps
+    out, lse, dq, dk, dv = got
+    for b, h in slices:
+        qc, kc, vc, dc = (t[b:b + 1, h:h + 1].cpu() for t in (q, k, v, do))
+        ic = index[b:b + 1, h:h + 1]
+        ro, rl = orc.attention_gathered(qc, kc, vc, ic, count, blk=blk)
+        assert (out[b, h].float().cpu() - ro[0, 0]).abs().max().item() <= 3e-2
+        assert (lse[b, h].cpu() - rl[0, 0]).abs().max().item() <= 2e-3
+        ref = orc.backward_gathered(qc, kc, vc, dc, ic, count, blk=blk)
+        pt = orc.backward_gathered(qc, kc, vc, dc, ic, count, blk=blk, upcast=False)
+        for name, g, r, p in zip(("dq", "dk", "dv"), (dq, dk, dv), ref, pt):
+            tol = 3 * (p - r).abs().max().item() + 3 * bf16_roundtrip_eps(r) + 5e-3
+            err = (g[b, h].float().cpu() - r[0, 0]).abs().max().item()
+            assert err <= tol, f"{name}[{b},{h}]: max err {err} > tol {tol}"
+
+
+def test_config2_fwd_bwd_full_size():
+    """B=2, H=32, S=32768, 26 of 256 blocks per row (the workload of bench.py): forward + backward through the
+    public entry points, sampled (batch, head) slices against the oracle, whole-tensor sanity and repeatability."""
+    from block_sparse_attention import bsa_attn_bwd, bsa_attn_fwd, check_device_status
+    B, H, S, count = 2, 32, 32768, 26
+    index = _uniform_index(B, H, S // 128, S // 128, count, 2000)
+    q, k, v, do = (_randn_bf16((B, H, S, 128), s) for s in (1, 2, 3, 4))
+    ic = index.cuda()
+    out, lse = bsa_attn_fwd(q, k, v, ic, count, return_lse=True, sparse_block_size=128)
+    dq, dk, dv = bsa_attn_bwd(do, q, k, v, out, lse, ic, count, sparse_block_size=128)
+    check_device_status()
+    for t in (out, lse, dq, dk, dv):
+        assert torch.isfinite(t.float()).all()
+    _check_fwd_bwd_slices(q, k, v, do, index, count, (out, lse, dq, dk, dv), [(0, 0), (1, 31)])
+    dq2, dk2, dv2 = bsa_attn_bwd(do, q, k, v, out, lse, ic, count, sparse_block_size=128)
+    assert torch.equal(dq, dq2) and torch.equal(dk, dk2) and torch.equal(dv, dv2)
+
+
+def test_backward_two_query_groups_at_default_bucket():
+    """S = 65536 gives 512 query blocks, above the default bucket of 384 (the reference's rule,
+    csrc/bwd/sm100_blk128/bsa_bwd_sm100.py:2162-2171): the dK/dV kernel walks the CSR rows of two query groups."""
+    from block_sparse_attention import bsa_attn_bwd, bsa_attn_fwd, check_device_status
+    from block_sparse_attention.bsa_attn_interface import sm100_blk128_bwd_default_bucketed_k2q_size_blocks
+    B, H, S, count = 1, 2, 65536, 8
+    Nq = S // 128
+    assert Nq > sm100_blk128_bwd_default_bucketed_k2q_size_blocks(Nq, H)
+    index = _uniform_index(B, H, Nq, Nq, count, 77)
+    q, k, v, do = (_randn_bf16((B, H, S, 128), s) for s in (5, 6, 7, 8))
+    ic = index.cuda()
+    out, lse = bsa_attn_fwd(q, k, v, ic, count, return_lse=True, sparse_block_size=128)
+    dq, dk, dv = bsa_attn_bwd(do, q, k, v, out, lse, ic, count, sparse_block_size=128)
+    check_device_status()
+    _check_fwd_bwd_slices(q, k, v, do, index, count, (out, lse, dq, dk, dv), [(0, 1)])
 
 
 def test_config3_gqa_packed_poisson_counts_full_size():

@@ -135,7 +135,7 @@ def test_boundary_counts_poisoned_index(blk, Sq, Sk):
     _check(out, lse, ref_out, ref_lse, q, k, v)
 
 
-@pytest.mark.parametrize("blk,rank", [(128, 1), (64, 1), (64, 2), (64, 3)])
+@pytest.mark.parametrize("blk,rank", [(128, 1), (128, 2), (128, 3), (64, 1), (64, 2), (64, 3)])
 def test_block_sizes_including_zero(blk, rank):
     q, k, v, index, nums, sizes = _random_case(5, 2, 2, 2, 512, 640, blk, [3, 5, 1, 2], sizes_rank=rank)
     out, lse = _fwd(*_cuda(q, k, v, index), 0, block_sizes=sizes.cuda(), q2k_block_nums=nums.cuda(),

@@ -175,6 +175,14 @@ def test_split_policy_matches_reference():
     assert orc.blk64_auto_kv_splits(1, 1, 64 * 100, 2048) == 8
 
 
+def test_fp8_split_policy_matches_reference():
+    """Grid generated by running the reference's _sm100_blk64_auto_fp8_kv_splits (tests/golden/make_golden.py)."""
+    rows = load_golden("policy_fp8_blk64_splits.npz")["rows"].tolist()
+    assert len(rows) > 1000
+    for kv_blocks, heads, seqlen_q, batch, num_sms, splits in rows:
+        assert orc.blk64_auto_fp8_kv_splits(kv_blocks, heads, seqlen_q, batch, num_sms) == splits
+
+
 def test_analytic_known_answers():
     """Known-answer rows in the style of tests/test_flash_fwd.py:1682-1722: q = 0 gives a uniform
     softmax, so out = mean(v) over the selected tokens and lse = log(number of selected tokens)."""
