@@ -109,7 +109,7 @@ class BwdArgs(ctypes.Structure):
         ("num_q_groups", ctypes.c_int32),
         ("bucket_size_blocks", ctypes.c_int32),
         ("softmax_scale", ctypes.c_float),
-        ("reserved", ctypes.c_int32),
+        ("stages", ctypes.c_int32),
     ]
 
 

@@ -668,6 +668,9 @@ def _build_bucketed_k2q_csr(
 # --------------------------------------------------------------------------------------------------
 # backward
 # --------------------------------------------------------------------------------------------------
+_last_bwd_workspace = {}  # profiling only: the workspace of the last call made with a `stages` mask, per device
+
+
 def bsa_attn_bwd(
     dout: torch.Tensor,
     q: torch.Tensor,
@@ -688,13 +691,22 @@ def bsa_attn_bwd(
     *,
     sparse_block_size: int = 64,
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Backward of ``bsa_attn_fwd``; see ``_bsa_attn_bwd`` (same arguments plus a profiling knob)."""
+    return _bsa_attn_bwd(dout, q, k, v, out, lse, q2k_block_index, block_sparse_num, block_sizes, q2k_block_nums,
+                         softmax_scale, dq, dk, dv, bucket_size_blocks, layout, sparse_block_size=sparse_block_size)
+
+
+def _bsa_attn_bwd(dout, q, k, v, out, lse, q2k_block_index, block_sparse_num, block_sizes=None, q2k_block_nums=None,
+                  softmax_scale=None, dq=None, dk=None, dv=None, bucket_size_blocks=None, layout="bhsd", *,
+                  sparse_block_size=64, stages=0):
     """Backward of ``bsa_attn_fwd`` (reference bsa_attn_interface.py:3759-3996; the 64-token driver is
     ``_bsa_attn_bwd_bucketed_k2q_csr`` :4022-4290): BF16, MHA, D = 128, 64- or 128-token blocks.  dQ, dK
     and dV are accumulated in tensor memory in a fixed order without atomics, so repeated calls are
     bit-identical.  ``block_sizes`` (rank 1 ``(num_kv_blocks,)`` or rank 2 ``(batch, num_kv_blocks)``)
     masks the tail tokens of KV blocks exactly as the forward does; the physical KV tail is always masked.
     The reference's 128-token backward ignores ``block_sizes``; with the full-block sizes its tests pass
-    the results are the same."""
+    the results are the same.  ``stages`` (0 = everything) is a mask of the three passes to launch - 1 preprocess,
+    2 dQ, 4 dK/dV - so that one pass can be timed alone after a full call has filled the workspace statistics."""
     assert sparse_block_size in (64, 128), f"sparse_block_size must be 64 or 128, got {sparse_block_size}"
     assert layout in ("bhsd", "bshd"), f"layout must be 'bhsd' or 'bshd', got {layout!r}"
     blk = sparse_block_size
@@ -763,7 +775,13 @@ def bsa_attn_bwd(
         q2k_block_index, block_sparse_num, Nkv, bucket_size_blocks=bucket_size_blocks,
         q2k_block_nums=q2k_block_nums)
     ws_bytes = int(lib.bsa_bwd_workspace_bytes(B, H, Sq, Sk, D))
-    workspace = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=device)
+    if stages not in (0, 7) and _last_bwd_workspace.get(device) is not None \
+            and _last_bwd_workspace[device].numel() == max(ws_bytes, 16):
+        workspace = _last_bwd_workspace[device]  # the row statistics of the full call before
+    else:
+        workspace = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=device)
+    if stages != 0:
+        _last_bwd_workspace[device] = workspace
 
     views = {}
     for name, t in (("dout", dob), ("q", qb), ("k", kb), ("v", vb), ("out", ob)):
@@ -807,6 +825,7 @@ def bsa_attn_bwd(
     a.num_q_groups = G
     a.bucket_size_blocks = int(bucket_size_blocks)
     a.softmax_scale = float(softmax_scale)
+    a.stages = int(stages)
     with torch.cuda.device(device):
         torch.cuda.nvtx.range_push("bsa_attn_bwd_bucketed_k2q_csr_kernel")
         try:

@@ -1120,6 +1120,15 @@ extern "C" int bsa_bwd(const bsa_bwd_args* a, void* cuda_stream) {
     if ((a->dq_stride[i] | a->dk_stride[i] | a->dv_stride[i] | a->o_stride[i] | a->do_stride[i]) % 8 != 0)
       return set_error(BSA_ERR_INVALID, "bsa_bwd: strides must be multiples of 8 elements");
   }
+  if (a->stages < 0 || a->stages > 7) return set_error(BSA_ERR_INVALID, "bsa_bwd: stages must be a mask of bits 0-2");
+  // the preprocess pass and the epilogues use 16-byte vector accesses on these tensors
+  {
+    const void* vec16[5] = {a->out, a->dout, a->dq, a->dk, a->dv};
+    const char* names[5] = {"out", "dout", "dq", "dk", "dv"};
+    for (int i = 0; i < 5; ++i)
+      if ((reinterpret_cast<uintptr_t>(vec16[i]) & 15u) != 0)
+        return set_error(BSA_ERR_INVALID, "%s: base address must be 16-byte aligned", names[i]);
+  }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
   int dev = 0;
   cudaGetDevice(&dev);
@@ -1128,16 +1137,9 @@ extern "C" int bsa_bwd(const bsa_bwd_args* a, void* cuda_stream) {
 
   const int blk = a->blk;
   const int Nq = (a->Sq + blk - 1) / blk, Nkv = (a->Sk + blk - 1) / blk;
-  const long long rows_pad = (long long)a->B * a->H * Nq * blk;
-  float* lse_log2 = reinterpret_cast<float*>(a->workspace);
-  float* delta = lse_log2 + rows_pad;
-  bwd_preprocess_kernel<<<(unsigned)((rows_pad + 8 * kPreRowsPerWarp - 1) / (8 * kPreRowsPerWarp)), 256, 0, st>>>(
-      reinterpret_cast<const __nv_bfloat16*>(a->out), reinterpret_cast<const __nv_bfloat16*>(a->dout), a->lse, lse_log2,
-      delta, a->o_stride[0], a->o_stride[1], a->o_stride[2], a->do_stride[0], a->do_stride[1], a->do_stride[2], a->H,
-      a->Sq, Nq * blk, rows_pad, a->D);
-  cudaError_t e = cudaGetLastError();
-  if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "bwd preprocess launch: %s", cudaGetErrorString(e));
-
+  const long long work_q = (long long)a->B * a->H * Nq, work_kv = (long long)a->B * a->H * Nkv;
+  if (work_q > 0x7fffffffLL || work_kv > 0x7fffffffLL) return set_error(BSA_ERR_UNSUPPORTED, "bsa_bwd: too many tiles");
+  // every argument is validated (tensor maps included) before the first launch
   CUtensorMap tq, tdo, tk, tv;
   {
     uint64_t qd[4] = {(uint64_t)a->D, (uint64_t)a->Sq, (uint64_t)a->H, (uint64_t)a->B};
@@ -1158,6 +1160,24 @@ extern "C" int bsa_bwd(const bsa_bwd_args* a, void* cuda_stream) {
     if ((rc = make_tensor_map(&tk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, a->k, kd, sb, box, "k"))) return rc;
     strides(a->v_stride, sb);
     if ((rc = make_tensor_map(&tv, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, a->v, kd, sb, box, "v"))) return rc;
+  }
+  auto* dq_kernel = blk == 128 ? bwd_dq_kernel<128> : bwd_dq_kernel<64>;
+  auto* dkv_kernel = blk == 128 ? bwd_dkv_kernel<128> : bwd_dkv_kernel<64>;
+  cudaError_t e = cudaFuncSetAttribute(dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmem);
+  if (e == cudaSuccess) e = cudaFuncSetAttribute(dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDkvSmem);
+  if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "bsa_bwd: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
+  const int stages = a->stages == 0 ? 7 : a->stages;
+
+  const long long rows_pad = (long long)a->B * a->H * Nq * blk;
+  float* lse_log2 = reinterpret_cast<float*>(a->workspace);
+  float* delta = lse_log2 + rows_pad;
+  if (stages & 1) {
+    bwd_preprocess_kernel<<<(unsigned)((rows_pad + 8 * kPreRowsPerWarp - 1) / (8 * kPreRowsPerWarp)), 256, 0, st>>>(
+        reinterpret_cast<const __nv_bfloat16*>(a->out), reinterpret_cast<const __nv_bfloat16*>(a->dout), a->lse, lse_log2,
+        delta, a->o_stride[0], a->o_stride[1], a->o_stride[2], a->do_stride[0], a->do_stride[1], a->do_stride[2], a->H,
+        a->Sq, Nq * blk, rows_pad, a->D);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "bwd preprocess launch: %s", cudaGetErrorString(e));
   }
   BwdParams p{};
   p.q2k_index = a->q2k_index;
@@ -1195,20 +1215,17 @@ extern "C" int bsa_bwd(const bsa_bwd_args* a, void* cuda_stream) {
   p.softmax_scale = a->softmax_scale;
   p.scale_log2 = a->softmax_scale * kLog2e;
 
-  auto* dq_kernel = blk == 128 ? bwd_dq_kernel<128> : bwd_dq_kernel<64>;
-  auto* dkv_kernel = blk == 128 ? bwd_dkv_kernel<128> : bwd_dkv_kernel<64>;
-  e = cudaFuncSetAttribute(dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmem);
-  if (e == cudaSuccess) e = cudaFuncSetAttribute(dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDkvSmem);
-  if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "bsa_bwd: cudaFuncSetAttribute: %s", cudaGetErrorString(e));
-  const long long work_q = (long long)a->B * a->H * Nq, work_kv = (long long)a->B * a->H * Nkv;
-  if (work_q > 0x7fffffffLL || work_kv > 0x7fffffffLL) return set_error(BSA_ERR_UNSUPPORTED, "bsa_bwd: too many tiles");
   const int grid_q = (int)(work_q < num_sms ? work_q : num_sms);
   const int grid_kv = (int)(work_kv < num_sms ? work_kv : num_sms);
-  dq_kernel<<<grid_q, kDqThreads, kDqSmem, st>>>(tq, tdo, tk, tv, p);
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "bwd dQ launch: %s", cudaGetErrorString(e));
-  dkv_kernel<<<grid_kv, kDkvThreads, kDkvSmem, st>>>(tq, tdo, tk, tv, p);
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "bwd dK/dV launch: %s", cudaGetErrorString(e));
+  if (stages & 2) {
+    dq_kernel<<<grid_q, kDqThreads, kDqSmem, st>>>(tq, tdo, tk, tv, p);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "bwd dQ launch: %s", cudaGetErrorString(e));
+  }
+  if (stages & 4) {
+    dkv_kernel<<<grid_kv, kDkvThreads, kDkvSmem, st>>>(tq, tdo, tk, tv, p);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "bwd dK/dV launch: %s", cudaGetErrorString(e));
+  }
   return BSA_OK;
 }

@@ -517,7 +517,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           for (int g = 0; g < 8; ++g) {
             const int jb = (BLK == 128 || g < 4) ? j0 : j1;
             const int gi = (BLK == 128) ? jb * 8 + g : jb * 4 + (g & 3);
-            ksc[g] = (jb >= 0 && gi < ngroups) ? ks[gi] * (q_row_scale * p.scale_log2) : 0.f;
+            ksc[g] = (jb >= 0 && jb < p.Nkv && gi < ngroups) ? ks[gi] * (q_row_scale * p.scale_log2) : 0.f;
           }
         }
 
@@ -955,7 +955,14 @@ extern "C" int bsa_fwd(const bsa_fwd_args* a, void* cuda_stream) {
   if (a->splits < 1 || a->splits > 256) return set_error(BSA_ERR_INVALID, "bsa_fwd: splits out of [1,256]");
   if (a->splits > 1 && (!a->partial_o || !a->partial_lse))
     return set_error(BSA_ERR_INVALID, "bsa_fwd: split run needs partial buffers");
-  if (a->splits == 1 && !a->out) return set_error(BSA_ERR_INVALID, "bsa_fwd: null out");
+  if (a->splits == 1) {
+    // the output tensor map needs a 16-byte aligned base and 16-byte strides; checked here, before any CUDA call
+    if (!a->out) return set_error(BSA_ERR_INVALID, "bsa_fwd: null out");
+    if ((reinterpret_cast<uintptr_t>(a->out) & 15u) != 0)
+      return set_error(BSA_ERR_INVALID, "out: base address must be 16-byte aligned");
+    if ((a->o_stride[0] | a->o_stride[1] | a->o_stride[2]) % 8 != 0)
+      return set_error(BSA_ERR_INVALID, "out: strides must be multiples of 8 elements");
+  }
   if (a->cap < 0 || a->block_sparse_num < 0) return set_error(BSA_ERR_INVALID, "bsa_fwd: negative count");
   const bool fp8 = a->dtype == BSA_DTYPE_E4M3;
   const int G = a->Hq / a->Hkv;

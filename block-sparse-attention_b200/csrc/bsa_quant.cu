@@ -7,6 +7,8 @@
 // Recipe of bsa_fp8_quant.py:10-104 (the Triton kernels behind quantize_sage_bhsd), pinned by
 // tests/test_bsa_fp8_quant.py:34-63.
 #include "bsa_b200.h"
+
+#include <atomic>
 #include "bsa_common.cuh"
 #include "bsa_host.h"
 
@@ -224,6 +226,14 @@ extern "C" int bsa_quantize_sage(const void* q, const void* k, const void* v, vo
     return set_error(BSA_ERR_INVALID, "bsa_quantize_sage: null pointer");
   if (B < 1 || H < 1 || Sq < 1 || Sk < 1) return set_error(BSA_ERR_INVALID, "bsa_quantize_sage: non-positive extent");
   if ((long long)B * H > 65535) return set_error(BSA_ERR_UNSUPPORTED, "bsa_quantize_sage: B*H above 65535");
+  {
+    // the kernels read and write these tensors through 16-byte vector accesses
+    const void* vec16[7] = {q, k, v, q8, k8, v8, k_mean};
+    const char* names[7] = {"q", "k", "v", "q8", "k8", "v8", "k_mean"};
+    for (int i = 0; i < 7; ++i)
+      if ((reinterpret_cast<uintptr_t>(vec16[i]) & 15u) != 0)
+        return set_error(BSA_ERR_INVALID, "bsa_quantize_sage: %s must be 16-byte aligned", names[i]);
+  }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(cuda_stream);
   const int chunks = (Sk + kStatChunk - 1) / kStatChunk;
   float* ksum = partials;
@@ -271,18 +281,20 @@ extern "C" int bsa_quantize_sage_static(const void* q, const void* k, const void
                      need, kStaticScratchFloats);
   // In host code the array's name is only a handle; the device address has to be asked for, once per
   // device, with that device current.  This first call per device is the set-up.
-  static float* scratch_of_device[64] = {nullptr};
+  // (atomic slots: two host threads making the first call on one device both look the address up and store the
+  // same value)
+  static std::atomic<float*> scratch_of_device[64];
   int dev = -1;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64)
     return set_error(BSA_ERR_CUDA, "bsa_quantize_sage_static: cannot identify the current device");
-  float* scratch = scratch_of_device[dev];
+  float* scratch = scratch_of_device[dev].load(std::memory_order_acquire);
   if (scratch == nullptr) {
     void* addr = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&addr, g_quant_scratch);
     if (e != cudaSuccess || addr == nullptr)
       return set_error(BSA_ERR_CUDA, "bsa_quantize_sage_static: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
     scratch = static_cast<float*>(addr);
-    scratch_of_device[dev] = scratch;
+    scratch_of_device[dev].store(scratch, std::memory_order_release);
   }
   // Every slot that is read has been written earlier in the same call (statistics kernel -> finish kernel
   // -> apply kernel), so nothing has to be cleared between calls.

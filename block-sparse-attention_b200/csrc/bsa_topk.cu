@@ -81,6 +81,7 @@ pooled_score_kernel(const float* __restrict__ qm, const float* __restrict__ km, 
 // ------------------------------------------------------------------------------------------------
 __device__ __forceinline__ uint32_t orderable(float f) {
   const uint32_t u = __float_as_uint(f);
+  if ((u & 0x7fffffffu) > 0x7f800000u) return 0xffffffffu;  // NaN of either sign ranks above +inf (torch.topk)
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 

@@ -152,7 +152,8 @@ int64_t bsa_quantize_sage_scratch_floats(int32_t B, int32_t H, int32_t Sk);
  *   limit   : B*H*(1 + 2*ceil(Sk/1024))*128 floats <= BSA_QUANTIZE_STATIC_SCRATCH_FLOATS (1 Mi);
  *             larger problems are rejected with BSA_ERR_WORKSPACE and must use bsa_quantize_sage.
  *   set-up  : the first call on each device looks the array's device address up; make that first call
- *             outside any stream capture.
+ *             outside any stream capture.  Host threads may make it concurrently: the per-device slot is an
+ *             atomic, and every thread that finds it empty stores the same address.
  *   sharing : all calls on a device use the same array.  Calls that can overlap on the GPU (different
  *             streams without ordering) race on it; serialise them.  No state has to be cleared between
  *             calls: every value read is written earlier in the same call.
@@ -279,7 +280,9 @@ typedef struct bsa_bwd_args {
   int32_t num_q_groups;
   int32_t bucket_size_blocks;
   float softmax_scale;
-  int32_t reserved;
+  int32_t stages; /* 0 = the whole backward; otherwise a mask of the passes to launch (bit 0 preprocess, bit 1 dQ,
+                     bit 2 dK/dV), for timing one pass alone - the main passes read the preprocess results of an
+                     earlier call from `workspace` */
 } bsa_bwd_args;
 
 int bsa_bwd(const bsa_bwd_args* args, void* cuda_stream);

@@ -73,6 +73,47 @@ def test_cpu_tensors_and_bad_arguments_raise_assertion_errors():
         bsa_fp8_fwd(q8, q8, q8, s, s, s, idx, 2, sparse_block_size=64, kv_splits=2)
 
 
+def test_c_entry_points_reject_misaligned_pointers_before_any_launch():
+    """The kernels use 16-byte vector accesses on several tensors: a C caller passing an unaligned pointer
+    gets BSA_ERR_INVALID from the argument check (no CUDA call has been made by then, so this runs without a GPU)."""
+    from block_sparse_attention import _cabi
+    lib = _cabi.load()
+    good, bad = 0x10000, 0x10008
+    a = _cabi.BwdArgs()
+    for name in ("dout", "q", "k", "v", "out", "lse", "dq", "dk", "dv", "q2k_index", "csr_offsets", "csr_indices",
+                 "workspace", "status"):
+        setattr(a, name, good)
+    a.blk, a.B, a.H, a.Sq, a.Sk, a.D, a.cap, a.block_sparse_num, a.num_q_groups = 128, 1, 1, 128, 128, 128, 1, 1, 1
+    a.workspace_bytes = int(lib.bsa_bwd_workspace_bytes(1, 1, 128, 128, 128))
+    for t in ("do_stride", "q_stride", "k_stride", "v_stride", "o_stride", "dq_stride", "dk_stride", "dv_stride"):
+        setattr(a, t, _cabi._c_i64x3(128 * 128, 128 * 128, 128))
+    for name in ("out", "dout", "dq", "dk", "dv"):
+        setattr(a, name, bad)
+        assert lib.bsa_bwd(a, None) == -1 and "16-byte aligned" in _cabi.last_error() and name in _cabi.last_error()
+        setattr(a, name, good)
+    a.stages = 8
+    assert lib.bsa_bwd(a, None) == -1 and "stages" in _cabi.last_error()
+    # quantiser: q, k, v, q8, k8, v8, k_mean
+    args = [good] * 11
+    for i in (0, 1, 2, 3, 4, 5, 9):
+        args[i] = bad
+        assert lib.bsa_quantize_sage(*args, 1, 1, 16, 16, None) == -1 and "16-byte aligned" in _cabi.last_error()
+        args[i] = good
+    # forward: the output rows are stored as 16-byte vectors
+    f = _cabi.FwdArgs()
+    for name in ("q", "k", "v", "out", "q2k_index", "status"):
+        setattr(f, name, good)
+    f.blk, f.B, f.Hq, f.Hkv, f.Sq, f.Sk, f.D, f.cap, f.block_sparse_num, f.splits = 128, 1, 1, 1, 128, 128, 128, 1, 1, 1
+    f.softmax_scale = 0.1
+    for t in ("q_stride", "k_stride", "v_stride", "o_stride"):
+        setattr(f, t, _cabi._c_i64x3(128 * 128, 128 * 128, 128))
+    f.out = bad
+    assert lib.bsa_fwd(f, None) == -1 and "16-byte aligned" in _cabi.last_error()
+    f.out = good
+    f.o_stride = _cabi._c_i64x3(128 * 128, 128 * 128, 100)
+    assert lib.bsa_fwd(f, None) == -1 and "multiples of 8" in _cabi.last_error()
+
+
 def test_quantiser_rejections_on_cpu():
     from block_sparse_attention import quantize_sage_bhsd
     x = torch.zeros(1, 2, 64, 128, dtype=torch.bfloat16)

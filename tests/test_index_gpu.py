@@ -62,6 +62,30 @@ def test_csr_long_rows_global_sort_path():
     _assert_csr(q2k, 2, 3, 2000, None)
 
 
+def test_csr_attention_sink_rows_at_the_default_bucket():
+    """One KV block (an attention sink) is selected by every query block: with the default 64-token bucket of
+    1152 query blocks its CSR row has 1152 entries in the first group and the rest in the second.  Rows of
+    that length are sorted by counting in shared memory; the build must stay in the tens of microseconds."""
+    from block_sparse_attention.bsa_attn_interface import _build_bucketed_k2q_csr
+    gen = torch.Generator().manual_seed(9)
+    Nq, Nkv = 1300, 40
+    others = torch.stack([torch.randperm(Nkv - 1, generator=gen)[:3] + 1 for _ in range(2 * Nq)]).reshape(1, 2, Nq, 3)
+    q2k = torch.cat([others[..., :1], torch.zeros(1, 2, Nq, 1, dtype=torch.long), others[..., 1:]], dim=-1).int()
+    _assert_csr(q2k, 4, Nkv, 1152, None)
+    dup = q2k.clone()
+    dup[0, 0, 5, 2] = 0  # a duplicated id stays a duplicate
+    _assert_csr(dup, 4, Nkv, 1152, None)
+    qc = q2k.cuda()
+    _build_bucketed_k2q_csr(qc, 4, Nkv, bucket_size_blocks=1152)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(10):
+        _build_bucketed_k2q_csr(qc, 4, Nkv, bucket_size_blocks=1152)
+    b.record()
+    torch.cuda.synchronize()
+    assert a.elapsed_time(b) / 10 < 1.0, "CSR build with 1152-entry rows took more than 1 ms"
+
+
 def test_q2k_to_k2q_set_semantics():
     from block_sparse_attention import convert_q2k_to_k2q
     gen = torch.Generator().manual_seed(2)

@@ -78,3 +78,28 @@ def test_static_scratch_quantiser_rejects_oversized_problems():
     rc = lib.bsa_quantize_sage_static(p, p, p, p, p, p, p, p, p, B, H, 128, Sk, torch.cuda.current_stream().cuda_stream)
     assert rc == -4  # BSA_ERR_WORKSPACE: nothing was launched
     assert "exceed the built-in scratch" in _cabi.last_error()
+
+
+def test_static_scratch_quantiser_at_the_limit():
+    """The largest problem the built-in scratch takes, and the first one it does not.  With Sk <= 1024 a call
+    needs 3 * B * H * 128 floats (a mean row and two statistics rows per (batch, head)), so 2730 heads fit
+    (1 048 320 of 1 048 576 floats) and 2731 do not (1 048 704); the limit cannot be met exactly because
+    1 + 2 * ceil(Sk / 1024) is odd."""
+    from block_sparse_attention import _cabi
+    lib = _cabi.load()
+    cap = 1 << 20
+    gen = torch.Generator().manual_seed(5)
+    H, S = 2730, 16
+    assert 3 * H * 128 <= cap < 3 * (H + 1) * 128
+    q = torch.randn(1, H + 1, S, 128, generator=gen).bfloat16().cuda()
+    k = (torch.randn(1, H + 1, S, 128, generator=gen) + 0.5).bfloat16().cuda()
+    v = torch.randn(1, H + 1, S, 128, generator=gen).bfloat16().cuda()
+    fit = tuple(t[:, :H].contiguous() for t in (q, k, v))
+    rc_s, got = _static(lib, *fit)
+    rc_r, ref = _regular(lib, *fit)
+    assert rc_s == 0 and rc_r == 0, _cabi.last_error()
+    torch.cuda.synchronize()
+    for name in ref:
+        assert torch.equal(got[name], ref[name]), name
+    rc, _ = _static(lib, q, k, v)
+    assert rc == -4 and "exceed the built-in scratch" in _cabi.last_error()
