@@ -612,19 +612,14 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 // ------------------------------------------------------------------------------------------------
 // 3. dK/dV kernel
 // ------------------------------------------------------------------------------------------------
-// smem: K | V | ring of 5 tiles (Q_i, dO_i alternating) | row statistics: lse [3][128], delta [2][128] f32 |
-// barriers | misc.  The lse row of a query tile travels with its Q stage and the delta row with its dO stage, so
-// the exponentials of a tile wait for nothing but S^T.
+// smem: K | V | ring of 5 tiles (Q_i, dO_i alternating) | row statistics [2][2][128] f32 | barriers | misc
 // Tensor memory: X @0 takes S^T_i and, once every compute thread holds S^T_i in registers, dP^T_i; once that is
 // in registers too, S^T_{i+1}.  Y @128 takes P^T_i and dS^T_i (bf16, 32 columns each per compute group), the
 // tensor-memory operands of dV @256 += P^T dO and dK @384 += dS^T Q.  No MMA result that iteration i+1 needs waits
 // for an MMA that consumes what the compute threads produce in iteration i.
 constexpr int kDkvStages = 5;
-// lse_{i+3} is loaded into the stage that dV_i releases, i.e. after the compute threads have finished with lse_i:
-// three slots; delta_{i+2} into the stage that dK_i releases: two slots.
-constexpr int kLseSlots = 3, kDeltaSlots = 2;
-constexpr int kStatBytes = (kLseSlots + kDeltaSlots) * 512;
-constexpr int kDkvSmem = 2 * kTile + kDkvStages * kTile + kStatBytes + BwdSmem::kBarBytes + BwdSmem::kMisc;
+constexpr int kStatSlots = 2;
+constexpr int kDkvSmem = 2 * kTile + kDkvStages * kTile + kStatSlots * 1024 + BwdSmem::kBarBytes + BwdSmem::kMisc;
 
 // BLK = 64: the KV block has 64 tokens (top half of the 128-row MMAs, lanes 64-127 idle) and one iteration
 // covers two CSR entries: their 64-row Q / dO tiles form one 128-row ring tile, so compute group g owns
@@ -638,9 +633,8 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   uint8_t* sK = smem_raw;
   uint8_t* sV = sK + kTile;
   uint8_t* sRing = sV + kTile;
-  float* sLse = reinterpret_cast<float*>(sRing + NS * kTile);  // [kLseSlots][128]  -lse * log2(e)
-  float* sDelta = sLse + kLseSlots * 128;                        // [kDeltaSlots][128]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sLse) + kStatBytes);
+  float* sStats = reinterpret_cast<float*>(sRing + NS * kTile);  // [slot][0: lse_log2, 1: delta][128]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(reinterpret_cast<uint8_t*>(sStats) + kStatSlots * 1024);
   uint32_t& s_tmem_base = *reinterpret_cast<uint32_t*>(bars + 32);
   volatile int& s_abort = *reinterpret_cast<volatile int*>(bars + 33);
   if ((smem_u32(smem_raw) & 1023u) != 0) {
@@ -725,20 +719,26 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           if (!mbar_wait(BAR(kREmpty + stage), ph ^ 1, wctx, 501)) return false;
           if (lane == 0) {
             const CUtensorMap* tm = which ? &tm_do : &tm_q;
-            mbar_arrive_expect_tx(BAR(kRFull + stage), kTile + 512);
+            mbar_arrive_expect_tx(BAR(kRFull + stage), kTile + (which ? 1024 : 0));
             for (int sl = 0; sl < 2; ++sl) {
               const uint32_t dst = smem_u32(sRing + stage * kTile + sl * kSlab);
               tma_load_4d(dst, tm, BAR(kRFull + stage), sl * 64, qa * BLK, h, b);
               if (BLK == 64) tma_load_4d(dst + 64 * 128, tm, BAR(kRFull + stage), sl * 64, qb * 64, h, b);
             }
-            // row statistics of the query rows: lse with the Q tile, delta with the dO tile
-            float* st = which ? sDelta + (tile_cnt % kDeltaSlots) * 128 : sLse + (tile_cnt % kLseSlots) * 128;
-            const float* src = (which ? p.delta : p.lse_log2) + (long long)bh * ((long long)p.Nq * BLK);
-            if (BLK == 128) {
-              bulk_load_1d(smem_u32(st), src + (long long)qa * 128, 512, BAR(kRFull + stage));
-            } else {
-              bulk_load_1d(smem_u32(st), src + (long long)qa * 64, 256, BAR(kRFull + stage));
-              bulk_load_1d(smem_u32(st + 64), src + (long long)qb * 64, 256, BAR(kRFull + stage));
+            if (which) {
+              // row statistics of the query rows travel with their dO tile: that stage is re-used only after
+              // dK of the tile two back, when the statistics slot of that tile is long free (two slots)
+              float* st = sStats + (tile_cnt % kStatSlots) * 256;
+              const long long plane = (long long)bh * ((long long)p.Nq * BLK);
+              if (BLK == 128) {
+                bulk_load_1d(smem_u32(st), p.lse_log2 + plane + (long long)qa * 128, 512, BAR(kRFull + stage));
+                bulk_load_1d(smem_u32(st + 128), p.delta + plane + (long long)qa * 128, 512, BAR(kRFull + stage));
+              } else {
+                bulk_load_1d(smem_u32(st), p.lse_log2 + plane + (long long)qa * 64, 256, BAR(kRFull + stage));
+                bulk_load_1d(smem_u32(st + 64), p.lse_log2 + plane + (long long)qb * 64, 256, BAR(kRFull + stage));
+                bulk_load_1d(smem_u32(st + 128), p.delta + plane + (long long)qa * 64, 256, BAR(kRFull + stage));
+                bulk_load_1d(smem_u32(st + 192), p.delta + plane + (long long)qb * 64, 256, BAR(kRFull + stage));
+              }
             }
           }
           ++r_cnt;
@@ -930,8 +930,8 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         continue;
       }
       for (int i = 0; i < T && ok; ++i) {
-        const float4* st_l = reinterpret_cast<const float4*>(sLse + (tile_cnt % kLseSlots) * 128 + grp * 64);
-        const float4* st_d = reinterpret_cast<const float4*>(sDelta + (tile_cnt % kDeltaSlots) * 128 + grp * 64);
+        const float4* st_l = reinterpret_cast<const float4*>(sStats + (tile_cnt % kStatSlots) * 256 + grp * 64);
+        const float4* st_d = reinterpret_cast<const float4*>(sStats + (tile_cnt % kStatSlots) * 256 + 128 + grp * 64);
         ++tile_cnt;
         // ---- phase 1: P^T = exp2(S^T*scale - lse[q]) -> bf16 -> Y
         PT_MARK(0)
@@ -956,10 +956,9 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           continue;
         }
         {
-          // observe the arrival of this tile's lse row directly (it was copied on the Q stage's barrier,
-          // which has completed: S^T_i is done); the phase cannot have advanced further: the stage is held
-          // until dK_i
-          const uint32_t pos = base + 2 * (uint32_t)i;
+          // observe the arrival of this tile's row statistics directly (they were copied on the dO
+          // stage's barrier); the phase cannot have advanced further: the stage is held until dV
+          const uint32_t pos = base + 2 * (uint32_t)i + 1;
           ok = mbar_wait(BAR(kRFull + pos % NS), (pos / NS) & 1, wctx, 523);
           if (!ok) break;
         }
@@ -1012,12 +1011,6 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (!ok) break;
         PT_MARK(3)
         ++dp_cnt;
-        {
-          // the delta row came with the dO tile, which dP^T_i has read: the wait only makes the copy visible
-          const uint32_t pos = base + 2 * (uint32_t)i + 1;
-          ok = mbar_wait(BAR(kRFull + pos % NS), (pos / NS) & 1, wctx, 525);
-          if (!ok) break;
-        }
         tc_fence_after();
         uint32_t dp[64];
         tmem_ld32(tX + lane_base + grp * 64, dp);
