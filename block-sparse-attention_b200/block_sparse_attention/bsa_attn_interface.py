@@ -643,8 +643,22 @@ def _build_bucketed_k2q_csr(
     q2k_block_nums: Optional[torch.Tensor] = None,
 ) -> Tuple[torch.Tensor, torch.Tensor, int, int]:
     """Bucketed k2q CSR (reference bsa_attn_interface.py:3999-4019): returns
-    ``(offsets [B,H,G,Nkv+1], indices [B,H,max(1,Nq*cap)], num_q_groups, num_kv_blocks)``.  Unlike the
-    reference every CSR row comes out in ascending q order, so the result is run-to-run identical."""
+    ``(offsets [B,H,G,Nkv+1], indices [B,H,max(1,Nq*W)], num_q_groups, num_kv_blocks)`` with ``W`` the fixed
+    ``block_sparse_num`` or, with per-row counts, the row width of the index - the reference's shapes.  Unlike
+    the reference every CSR row comes out in ascending q order, so the result is run-to-run identical."""
+    offsets, indices, G = _build_k2q_csr_full(q2k_block_index, block_sparse_num, num_kv_blocks, bucket_size_blocks,
+                                              q2k_block_nums)
+    has_nums = q2k_block_nums is not None and q2k_block_nums.numel() > 0
+    if not has_nums:
+        Nq, cap = q2k_block_index.shape[2], q2k_block_index.shape[3]
+        assert 0 <= block_sparse_num <= cap, (
+            f"block_sparse_num ({block_sparse_num}) must not exceed the index row width ({cap})")
+        indices = indices[..., :max(1, Nq * int(block_sparse_num))]
+    return offsets, indices, G, int(num_kv_blocks)
+
+
+def _build_k2q_csr_full(q2k_block_index, block_sparse_num, num_kv_blocks, bucket_size_blocks, q2k_block_nums):
+    """The CSR with ``indices`` at its full allocation ``[B,H,max(1,Nq*cap)]`` (what ``bsa_bwd`` addresses)."""
     assert q2k_block_index.is_cuda and q2k_block_index.dtype == torch.int32 and q2k_block_index.ndim == 4
     assert bucket_size_blocks >= 1
     lib = _cabi.load()
@@ -662,7 +676,7 @@ def _build_bucketed_k2q_csr(
                                           int(block_sparse_num), B, H, Nq, cap, int(num_kv_blocks),
                                           int(bucket_size_blocks), offsets.data_ptr(), indices.data_ptr(),
                                           _cabi.stream_ptr(q2k.device)), "bsa_build_k2q_csr")
-    return offsets, indices, G, int(num_kv_blocks)
+    return offsets, indices, G
 
 
 # --------------------------------------------------------------------------------------------------
@@ -771,9 +785,8 @@ def _bsa_attn_bwd(dout, q, k, v, out, lse, q2k_block_index, block_sparse_num, bl
     dqb, dkb, dvb = tr(dq_t), tr(dk_t), tr(dv_t)
 
     lib = _cabi.load()
-    offsets, indices, G, _ = _build_bucketed_k2q_csr(
-        q2k_block_index, block_sparse_num, Nkv, bucket_size_blocks=bucket_size_blocks,
-        q2k_block_nums=q2k_block_nums)
+    offsets, indices, G = _build_k2q_csr_full(q2k_block_index, block_sparse_num, Nkv, bucket_size_blocks,
+                                              q2k_block_nums)
     ws_bytes = int(lib.bsa_bwd_workspace_bytes(B, H, Sq, Sk, D))
     if stages not in (0, 7) and _last_bwd_workspace.get(device) is not None \
             and _last_bwd_workspace[device].numel() == max(ws_bytes, 16):

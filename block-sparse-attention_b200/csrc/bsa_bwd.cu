@@ -181,7 +181,8 @@ __device__ __forceinline__ void store_row_half(__nv_bfloat16* dst, const uint32_
 }
 
 constexpr uint32_t kIdescKK = umma_idesc(1, 1, 0, 0, 128, 128);   // A K-major, B K-major
-constexpr uint32_t kIdescKMN = umma_idesc(1, 1, 0, 1, 128, 128);  // A K-major (smem or tmem), B MN-major
+// A K-major (smem or tmem), B MN-major with n output columns: the gradients of a 64-wide head take 64-column MMAs
+__device__ __forceinline__ uint32_t idesc_kmn(int n) { return umma_idesc(1, 1, 0, 1, 128, (uint32_t)n); }
 
 // The helpers below take ready-made descriptors (built once per kernel); a byte offset b inside a tile is
 // an addition of b >> 4 to the descriptor's low word.
@@ -189,30 +190,24 @@ __device__ __forceinline__ uint64_t desc_k_major(uint32_t saddr) { return umma_d
 __device__ __forceinline__ uint64_t desc_mn_major(uint32_t saddr) { return umma_desc_sw128(saddr, kSlab, 1024); }
 constexpr uint64_t kTileDescStep = kTile >> 4;  // descriptor distance between consecutive ring tiles
 
-// D = A(smem, K-major) * B(smem, K-major)^T over the 128-deep contraction: 8 k-steps across two slabs
+// D = A(smem, K-major) * B(smem, K-major)^T over the head dimension: `ksteps` = D / 16 k-steps across two slabs
+// (a 64-wide head contracts over the first slab only; the zero-filled second one is never read).
 // All helpers are called by the whole (converged) issuing warp; only the lane with led != 0 issues.
-__device__ __forceinline__ void mma_ss_kk(uint32_t d, uint64_t a_desc, uint64_t b_desc, bool acc, uint32_t led) {
+__device__ __forceinline__ void mma_ss_kk(uint32_t d, uint64_t a_desc, uint64_t b_desc, bool acc, uint32_t led,
+                                          int ksteps) {
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     const uint64_t off = (uint64_t)((k >> 2) * (kSlab >> 4) + (k & 3) * 2);
-    umma_f16_ss_led(d, a_desc + off, b_desc + off, kIdescKK, (acc || k > 0) ? 1u : 0u, led);
-  }
-}
-// D (+)= A(smem, K-major [rows][contraction]) * B(smem tile [contraction rows][128 channels], MN-major)
-__device__ __forceinline__ void mma_ss_kmn(uint32_t d, uint64_t a_desc, uint64_t b_desc_mn, bool acc, uint32_t led) {
-#pragma unroll
-  for (int k = 0; k < 8; ++k) {
-    const uint64_t aoff = (uint64_t)((k >> 2) * (kSlab >> 4) + (k & 3) * 2);
-    umma_f16_ss_led(d, a_desc + aoff, b_desc_mn + (uint64_t)(k * 128), kIdescKMN, (acc || k > 0) ? 1u : 0u, led);
+    umma_f16_ss_led(d, a_desc + off, b_desc + off, kIdescKK, (acc || k > 0) ? 1u : 0u, (k < ksteps) ? led : 0u);
   }
 }
 // D (+)= A(tmem bf16, two 32-column halves at a_lo / a_hi) * B(smem MN-major)
 __device__ __forceinline__ void mma_ts_kmn(uint32_t d, uint32_t a_lo, uint32_t a_hi, uint64_t b_desc_mn, bool acc,
-                                           uint32_t led) {
+                                           uint32_t led, uint32_t idesc) {
 #pragma unroll
   for (int k = 0; k < 8; ++k) {
     const uint32_t a = (k < 4) ? (a_lo + (uint32_t)k * 8u) : (a_hi + (uint32_t)(k - 4) * 8u);
-    umma_f16_ts_led(d, a, b_desc_mn + (uint64_t)(k * 128), kIdescKMN, (acc || k > 0) ? 1u : 0u, led);
+    umma_f16_ts_led(d, a, b_desc_mn + (uint64_t)(k * 128), idesc, (acc || k > 0) ? 1u : 0u, led);
   }
 }
 
@@ -362,6 +357,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
     bool first_tile = true;
     const uint32_t led = lane == 0;  // the whole warp runs the issue code, this lane issues
     const uint64_t ring_k = desc_k_major(smem_u32(sRing)), ring_mn = desc_mn_major(smem_u32(sRing));
+    const int ksteps = p.D / 16;              // contraction steps of S and dP
+    const uint32_t idesc_n = idesc_kmn(p.D);  // dQ has D columns
     PT_DECL
     for (int band = 0; band * (int)gridDim.x < num_work && ok; ++band) {
       const int w = bwd_work_at(p.order_q, band, num_work, p.status);
@@ -400,7 +397,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           tc_fence_after();
           {
             const uint32_t sk = stage_of(base + 2 * j);
-            mma_ss_kk(tS, q_desc, ring_k + sk * kTileDescStep, false, led);
+            mma_ss_kk(tS, q_desc, ring_k + sk * kTileDescStep, false, led, ksteps);
             umma_commit_led(BAR(kSFull), led);
             umma_commit_led(BAR(kREmpty + sk), led);
             if (j == n - 1) umma_commit_led(BAR(kQEmpty), led);  // the tile's last S: Q may be replaced
@@ -429,7 +426,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
           tc_fence_after();
           {
             const uint32_t sv = stage_of(base + 2 * j + 1);
-            mma_ss_kk(tdP + buf * 128u, do_desc, ring_k + sv * kTileDescStep, false, led);
+            mma_ss_kk(tdP + buf * 128u, do_desc, ring_k + sv * kTileDescStep, false, led, ksteps);
             umma_commit_led(BAR(kDpFull + buf), led);
             umma_commit_led(BAR(kREmpty + sv), led);
             if (j == n - 1) umma_commit_led(BAR(kDoEmpty), led);  // the tile's last dP: dO may be replaced
@@ -461,7 +458,7 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
             // dQ += dS_j (bf16 in tensor memory, at the head of each group's half of the buffer) * K_j
             // (MN-major view of the K tile)
             const uint32_t t = tdP + buf * 128u;
-            mma_ts_kmn(tdQ, t, t + 64u, ring_mn + sk * kTileDescStep, j > 0, led);
+            mma_ts_kmn(tdQ, t, t + 64u, ring_mn + sk * kTileDescStep, j > 0, led, idesc_n);
             umma_commit_led(BAR(kDsUsed + buf), led);
             umma_commit_led(BAR(kREmpty + sk), led);
           }
@@ -781,6 +778,8 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     bool ok = true, first_item = true;
     const uint64_t k_desc = desc_k_major(smem_u32(sK)), v_desc = desc_k_major(smem_u32(sV));
     const uint64_t ring_k = desc_k_major(smem_u32(sRing)), ring_mn = desc_mn_major(smem_u32(sRing));
+    const int ksteps = p.D / 16;              // contraction steps of S^T and dP^T
+    const uint32_t idesc_n = idesc_kmn(p.D);  // dK and dV have D columns
     PT_DECL
     for (int band = 0; band * (int)gridDim.x < num_work && ok; ++band) {
       const int w = bwd_work_at(p.order_kv, band, num_work, p.status);
@@ -822,7 +821,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         auto issue_dv = [&](int i) -> bool {  // after x_ready() has seen dP^T_i consumed
           if (i == 0 && !wait_free()) return false;
           const uint32_t sd = stage_of(base + 2 * i + 1);
-          mma_ts_kmn(tdV, tY, tY + 64u, ring_mn + sd * kTileDescStep, i > 0, led);  // dV += P^T_i dO_i
+          mma_ts_kmn(tdV, tY, tY + 64u, ring_mn + sd * kTileDescStep, i > 0, led, idesc_n);  // dV += P^T_i dO_i
           umma_commit_led(BAR(kREmpty + sd), led);
           umma_commit_led(BAR(kYFree), led);
           __syncwarp();
@@ -834,7 +833,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           if (!ok) break;
           {
             const uint32_t sq = stage_of(base + 2 * i);
-            mma_ss_kk(tX, k_desc, ring_k + sq * kTileDescStep, false, led);  // S^T_i
+            mma_ss_kk(tX, k_desc, ring_k + sq * kTileDescStep, false, led, ksteps);  // S^T_i
             umma_commit_led(BAR(kSFull), led);
             umma_commit_led(BAR(kREmpty + sq), led);
             ++x_issued;
@@ -849,7 +848,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           if (!ok) break;
           {
             const uint32_t sd = stage_of(base + 2 * i + 1);
-            mma_ss_kk(tX, v_desc, ring_k + sd * kTileDescStep, false, led);  // dP^T_i
+            mma_ss_kk(tX, v_desc, ring_k + sd * kTileDescStep, false, led, ksteps);  // dP^T_i
             umma_commit_led(BAR(kDpFull), led);
             ++x_issued;
           }
@@ -877,7 +876,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           tc_fence_after();
           {
             const uint32_t sq = stage_of(base + 2 * i);
-            mma_ts_kmn(tdK, tY + 32u, tY + 96u, ring_mn + sq * kTileDescStep, i > 0, led);  // dK += dS^T Q_i
+            mma_ts_kmn(tdK, tY + 32u, tY + 96u, ring_mn + sq * kTileDescStep, i > 0, led, idesc_n);  // dK += dS^T Q_i
             umma_commit_led(BAR(kREmpty + sq), led);
             umma_commit_led(BAR(kYFree), led);
           }

@@ -320,7 +320,11 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const uint32_t tS_s = tmem + 128u * (uint32_t)s, tO_s = tmem + 256u + 128u * (uint32_t)s;
     const uint32_t kFmt = (FP8 || p.f16) ? 0u : 1u;  // e4m3 (kind::f8f6f4) or f16 (kind::f16) = 0, bf16 = 1
     const uint32_t idesc_qk = umma_idesc(kFmt, kFmt, 0, 0, 128, 128);
-    const uint32_t idesc_pv = umma_idesc(kFmt, kFmt, 0, 1, 128, 128);
+    // Narrower heads (D = 64 or 96, 16-bit inputs only) use the head's own tile shape: QK^T contracts over D / 16
+    // k steps (the tensor maps zero-fill the rest of the 128-wide shared-memory tiles, which is then never read) and
+    // PV produces D output columns.
+    const uint32_t idesc_pv = umma_idesc(kFmt, kFmt, 0, 1, 128, (uint32_t)p.D);
+    const int qk_steps = FP8 ? Cfg::kKSteps : p.D / 16;
     uint32_t ring_pos = 0, q_cnt = 0, p_cnt = 0;  // ring_pos: tiles of this stream's ring consumed so far
     const uint32_t ring_depth = s ? (uint32_t)(NS - Cfg::kRing0) : (uint32_t)Cfg::kRing0;
     const uint32_t ring_first = s ? (uint32_t)Cfg::kRing0 : 0u;
@@ -368,7 +372,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           for (int k = 0; k < Cfg::kKSteps; ++k) {
             const uint64_t off = FP8 ? (uint64_t)(k * 2) : (uint64_t)((k >> 2) * (Cfg::kSlabBytes >> 4) + (k & 3) * 2);
             if (FP8) umma_f8_ss_led(tS_s, q_desc + off, kd + off, idesc_qk, k > 0, led);
-            else umma_f16_ss_led(tS_s, q_desc + off, kd + off, idesc_qk, k > 0, led);
+            else umma_f16_ss_led(tS_s, q_desc + off, kd + off, idesc_qk, k > 0, (k < qk_steps) ? led : 0u);
           }
           umma_commit_led(BAR(kSFull + s), led);
           umma_commit_led(BAR(kKvEmpty + stage), led);

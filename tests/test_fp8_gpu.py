@@ -150,3 +150,26 @@ def test_blk64_entry_point(Sq, Sk, topk, variable, sizes_mode):
     ref = orc.attention_gathered(*deq, index, topk, nums=nums, sizes=sizes, blk=64, return_lse=False)
     rel, mx = orc.fp8_accuracy(o, ref)
     assert mx < 0.15 and rel < 0.029, (rel, mx)
+
+
+def test_blk64_short_q_call_is_split_by_the_automatic_policy():
+    """Two query tiles cannot fill 148 SMs: the FP8 policy of the reference (bsa_attn_interface.py:693-718) splits
+    the KV range (16 ways at 256 blocks per row); the result must agree with the single-split run and the oracle."""
+    from block_sparse_attention import _cabi, bsa_fp8_blk64_fwd, quantize_sage_bhsd
+    from block_sparse_attention import bsa_attn_interface as iface
+    gen = torch.Generator().manual_seed(77)
+    B, H, Sq, Sk, topk = 1, 2, 64, 64 * 256, 256
+    q = torch.randn(B, H, Sq, 128, generator=gen).bfloat16()
+    k = (torch.randn(B, H, Sk, 128, generator=gen) + torch.randn(1, 1, 1, 128, generator=gen)).bfloat16()
+    v = torch.randn(B, H, Sk, 128, generator=gen).bfloat16()
+    index = torch.stack([torch.randperm(256, generator=gen) for _ in range(B * H)]).reshape(B, H, 1, 256).int()
+    sms = _cabi.load().bsa_num_sms(0)
+    assert iface._sm100_blk64_auto_fp8_kv_splits(topk, H, Sq, B, sms) > 1
+    quant = quantize_sage_bhsd(q.cuda(), k.cuda(), v.cuda())
+    out = bsa_fp8_blk64_fwd(*quant, index.cuda(), topk)
+    one = iface._bsa_fp8_blk128_fwd(*quant, index.cuda(), topk, None, None, None, 1, blk=64)
+    assert torch.allclose(out.float(), one.float(), atol=3e-2, rtol=3e-2)
+    deq = orc.sage_dequantize(*(t.cpu() for t in quant))
+    ref = orc.attention_gathered(*deq, index, topk, blk=64, return_lse=False)
+    rel, mx = orc.fp8_accuracy(out.float().cpu(), ref)
+    assert mx < 0.15 and rel < 0.029, (rel, mx)

@@ -16,7 +16,8 @@ def _assert_csr(q2k, bsn, nkv, bucket, nums):
     exp_off, exp_rows = orc.bucketed_k2q_csr(q2k, bsn, nkv, bucket, nums)
     assert offsets.dtype == torch.int32 and indices.dtype == torch.int32
     assert G == exp_off.shape[2] and rows_per_group == nkv
-    assert indices.shape[-1] == max(1, q2k.shape[2] * q2k.shape[3])
+    width = q2k.shape[3] if nums is not None else bsn  # the reference's shapes (bsa_attn_interface.py:3999-4019)
+    assert indices.shape[-1] == max(1, q2k.shape[2] * width)
     assert torch.equal(offsets.cpu(), exp_off)
     off, idx = offsets.cpu(), indices.cpu()
     B, H = off.shape[:2]
@@ -53,6 +54,8 @@ def test_csr_config2_shape_deterministic():
     from block_sparse_attention.bsa_attn_interface import _build_bucketed_k2q_csr
     o3, i3, _, _ = _build_bucketed_k2q_csr(q2k.cuda(), 26, 256, bucket_size_blocks=384)
     assert torch.equal(o1, o3) and torch.equal(i1[..., :256 * 26], i3[..., :256 * 26])
+    with pytest.raises(AssertionError):
+        _build_bucketed_k2q_csr(q2k.cuda(), 27, 256, bucket_size_blocks=384)  # count above the row width
 
 
 def test_csr_long_rows_global_sort_path():
