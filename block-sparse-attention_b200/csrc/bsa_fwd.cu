@@ -1,16 +1,18 @@
 // Block-sparse attention forward for sm_100a: TMA gathers of the K/V blocks named by the q2k index,
 // tcgen05 QK^T and PV MMAs accumulating in tensor memory, online softmax with LSE.
 //
-// One persistent CTA per SM walks (q tile, split) work items.  Warp roles:
-//   warps 0-3   softmax group 0: owns stream 0 (KV iterations 0, 2, 4, ...), one thread per query row
-//   warps 4-7   softmax group 1: owns stream 1 (KV iterations 1, 3, 5, ...)
-//   warps 8-9   MMA issue, one warp (one lane) per stream
-//   warps 10-11 TMA producers, one warp (one lane) per stream; producer 0 also loads the Q tiles
-// The four non-softmax warps give registers up (setmaxnreg) in favour of the softmax groups.
-// Tensor memory (512 columns): S0 @0, S1 @128, O0 @256, O1 @384 (fp32, 128 lanes x 128 columns each);
-// the probabilities P_s overwrite the head of S_s (bf16: 64 columns, e4m3: 32 columns) and are the
-// A operand of the PV MMA straight from tensor memory.  The two streams keep independent running
-// (max, sum, O) and are merged once per tile in the epilogue.
+// Two persistent CTAs per SM, each walking (q tile, split) work items on its own: while one CTA's softmax
+// works on a score tile, the tensor pipe runs the other CTA's MMAs, and a tile boundary (epilogue, first loads)
+// of one CTA is covered by the steady state of the other.  Warp roles of a CTA (256 threads):
+//   warps 0-3   softmax: one thread per query row (= tensor-memory lane), all 128 score columns of the row
+//   warp  4     MMA issue (one lane): QK(0), then PV(i), QK(i+1) per KV iteration
+//   warp  5     TMA producer (one lane): Q tile and the K/V ring in consumption order K(0), V(0), K(1), ...
+//   warps 6-7   idle; they complete the second warpgroup, whose four warps hand their registers to the softmax
+//               warps (setmaxnreg is a warpgroup-wide operation)
+// Tensor memory: 256 of the SM's 512 columns per CTA, S @0 and O @128 (fp32, 128 lanes x 128 columns each);
+// the probabilities P overwrite the head of S (bf16: 64 columns, e4m3: 32 columns) and are the A operand of
+// the PV MMA straight from tensor memory.  S(i+1) is issued behind PV(i) and so may overwrite P(i).
+// The output rows leave tensor memory through registers straight to global memory (a thread owns a whole row).
 //
 // A "KV iteration" is one 128-token tile: one 128-block, or two gathered 64-blocks (the second may be a
 // masked phantom when the count is odd).  With 64-token blocks the query tile has 64 rows and sits in
@@ -44,6 +46,8 @@ struct FwdParams {
   const float* __restrict__ q_scale;
   const float* __restrict__ k_scale;
   const float* __restrict__ v_scale;
+  uint8_t* out;  // 16-bit output, rows of D elements
+  long long o_stride_b, o_stride_h, o_stride_s;  // bytes
   float* lse;
   float* partial_o;
   float* partial_lse;
@@ -59,11 +63,11 @@ struct FwdParams {
   float scale_log2;
 };
 
-constexpr int kThreads = 384;
-constexpr int kSoftmaxThreads = 256;
-constexpr int kMmaWarp = 8;
-constexpr int kLoadWarp = 10;  // warps 8 and 9 issue the MMAs of stream 0 and 1, warps 10 and 11 load their K/V tiles
-
+constexpr int kThreads = 256;  // warps 6 and 7 only complete the second warpgroup (register re-balancing is per warpgroup)
+constexpr int kSoftmaxThreads = 128;  // warps 0-3: one thread per query row
+constexpr int kMmaWarp = 4;           // issues every MMA of the CTA
+constexpr int kLoadWarp = 5;          // TMA producer
+constexpr int kCtasPerSm = 2;
 
 template <bool FP8>
 struct FwdCfg {
@@ -71,19 +75,17 @@ struct FwdCfg {
   static constexpr int kTileBytes = 128 * 128 * kElt;  // one Q / K / V tile
   static constexpr int kSlabs = FP8 ? 1 : 2;           // 128-byte-wide column slabs per tile
   static constexpr int kSlabBytes = 128 * 128;         // 128 rows x 128 B
-  static constexpr int kStages = 4;
-  // each stream owns a private ring of K/V stages (stream 0 the first kRing0 stages), consumed strictly in
-  // order by that stream's issuing warp: a parity wait is then never more than one phase behind.
-  // Two stages per stream (the K and the V tile of one iteration) measured faster than deeper rings on every
-  // workload (cfg2 3.54 -> 3.42 ms against 3 + 2 stages; e4m3 1.64 -> 1.61 ms against 4 + 4)
-  static constexpr int kRing0 = 2;
-  static constexpr int kOBytes = 128 * 128 * 2;  // bf16 output staging
+  // One ring of K/V stages in consumption order K(0), V(0), K(1), V(1), ...  Two CTAs share an SM, so a CTA may
+  // take half of its shared memory: Q + two stages for 16-bit inputs, Q + four stages for e4m3.
+  static constexpr int kStages = FP8 ? 4 : 2;
   static constexpr int kMmaK = FP8 ? 32 : 16;
   static constexpr int kKSteps = 128 / kMmaK;
-  static constexpr int kPColsPerStep = FP8 ? 8 : 8;  // tensor-memory columns of P per MMA k step
-  // smem: Q | O | KV stages | 32 barriers | stats [2][128] float2 | tmem base, abort flag | 2 turn barriers
-  static constexpr int kSmemBytes = kTileBytes + kOBytes + kStages * kTileBytes + 256 + 2048 + 16 + 16;
+  static constexpr int kPColsPerStep = 8;  // tensor-memory columns of P per MMA k step
+  // smem: Q | KV stages | 32 barriers | tmem base, abort flag
+  static constexpr int kSmemBytes = kTileBytes + kStages * kTileBytes + 256 + 16;
 };
+// two CTAs (plus 1 KB each that the system reserves) must fit the 196 KB carve-out, which leaves the L1 60 KB
+static_assert(kCtasPerSm * (FwdCfg<false>::kSmemBytes + 1024) <= 196 * 1024, "two CTAs per SM");
 
 struct WorkItem {
   int b, hidx, m, split;
@@ -147,32 +149,24 @@ __device__ __forceinline__ int block_len(const FwdParams& p, int b, int h, int j
 }
 
 template <int BLK, bool FP8, bool SPLIT>
-__global__ void __launch_bounds__(kThreads, 1)
+__global__ void __launch_bounds__(kThreads, kCtasPerSm)
 bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
-               const __grid_constant__ CUtensorMap tm_v, const __grid_constant__ CUtensorMap tm_o,
-               const FwdParams p) {
+               const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
   using Cfg = FwdCfg<FP8>;
   constexpr int NS = Cfg::kStages;
   // everything lives in dynamic shared memory (no static allocation), so the 1024-byte alignment the
   // swizzled tiles need comes from the declaration itself and no slack has to be reserved
   extern __shared__ __align__(1024) uint8_t smem_raw[];
-  uint8_t* smem = smem_raw;
-  uint8_t* sQ = smem;
-  uint8_t* sO = sQ + Cfg::kTileBytes;
-  uint8_t* sKV = sO + Cfg::kOBytes;
+  uint8_t* sQ = smem_raw;
+  uint8_t* sKV = sQ + Cfg::kTileBytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + NS * Cfg::kTileBytes);
-  // barrier slots
-  //  0: q_full  1: q_empty  2..2+NS: kv_full  2+NS..2+2NS: kv_empty
-  //  then s_full[2], p_full[2], o_final
   const uint32_t bar_base = smem_u32(bars);
   auto BAR = [&](int i) { return bar_base + (uint32_t)i * 8u; };
-  constexpr int kQFull = 0, kQEmpty = 1, kKvFull = 2, kKvEmpty = 2 + NS, kSFull = 2 + 2 * NS,
-                kPFull = kSFull + 2, kOFinal = kPFull + 2, kEpiA = kOFinal + 2, kGrpB = kEpiA + 1,
-                kPHalf = kGrpB + 2, kNumBars = kPHalf + 2;
-  float2 (*s_stats)[128] = reinterpret_cast<float2 (*)[128]>(bars + 32);  // [2][128] (max, sum)
-  uint32_t& s_tmem_base = *reinterpret_cast<uint32_t*>(bars + 32 + 256);
-  volatile int& s_abort = *reinterpret_cast<volatile int*>(bars + 32 + 256 + 1);
-  const uint32_t turn_base = smem_u32(bars + 32 + 256 + 2);  // two more barriers: the issuers' turn tokens
+  constexpr int kQFull = 0, kQEmpty = 1, kKvFull = 2, kKvEmpty = 2 + NS, kSFull = 2 + 2 * NS, kPHalf = kSFull + 1,
+                kPFull = kPHalf + 1, kOFinal = kPFull + 1, kNumBars = kOFinal + 1;
+  static_assert(kNumBars <= 32, "barrier slots");
+  uint32_t& s_tmem_base = *reinterpret_cast<uint32_t*>(bars + 32);
+  volatile int& s_abort = *reinterpret_cast<volatile int*>(bars + 33);
   if ((smem_u32(smem_raw) & 1023u) != 0) {  // uniform over the CTA: nothing has been set up yet
     if (threadIdx.x == 0 && atomicCAS(p.status, 0, (int)kStatusBadIndex) == 0) p.status[2] = 999;
     return;
@@ -185,54 +179,41 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   if (threadIdx.x == 0) {
     s_abort = 0;
     mbar_init(BAR(kQFull), 1);
-    mbar_init(BAR(kQEmpty), 2);
+    mbar_init(BAR(kQEmpty), 1);
     for (int i = 0; i < NS; ++i) {
       mbar_init(BAR(kKvFull + i), 1);
       mbar_init(BAR(kKvEmpty + i), 1);
     }
-    for (int s = 0; s < 2; ++s) {
-      mbar_init(BAR(kSFull + s), 1);
-      // every softmax thread arrives itself: measured faster than one elected arrival per warp
-      mbar_init(BAR(kPFull + s), 128);
-      mbar_init(BAR(kPHalf + s), 128);
-    }
-    mbar_init(turn_base, 1);
-    mbar_init(turn_base + 8, 1);
-    mbar_init(BAR(kOFinal), 1);  // one per stream: a stream without work in a tile neither arrives nor is waited for
-    mbar_init(BAR(kOFinal + 1), 1);
-    mbar_init(BAR(kEpiA), kSoftmaxThreads);
-    mbar_init(BAR(kGrpB), kSoftmaxThreads);
+    mbar_init(BAR(kSFull), 1);
+    // every softmax thread arrives itself: measured faster than one elected arrival per warp
+    mbar_init(BAR(kPHalf), kSoftmaxThreads);
+    mbar_init(BAR(kPFull), kSoftmaxThreads);
+    mbar_init(BAR(kOFinal), 1);
     mbar_fence_init();
     fence_proxy_async_smem();
   }
-  static_assert(kNumBars <= 32, "barrier slots");
   if (warp == kMmaWarp) {
-    tmem_alloc(smem_u32(&s_tmem_base), 512);
+    // half of the SM's tensor memory: the other half belongs to the CTA that shares the SM
+    tmem_alloc(smem_u32(&s_tmem_base), 256);
     tmem_relinquish();
   }
   if (warp == kLoadWarp && lane == 0) {
     tma_prefetch_desc(&tm_q);
     tma_prefetch_desc(&tm_k);
     tma_prefetch_desc(&tm_v);
-    if (!SPLIT) tma_prefetch_desc(&tm_o);
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = s_tmem_base;
-  const uint32_t tS[2] = {tmem + 0u, tmem + 128u};
-  const uint32_t tO[2] = {tmem + 256u, tmem + 384u};
+  const uint32_t tS = tmem, tO = tmem + 128u;  // S (fp32; P overwrites its head) and O, 128 columns each
 
   const int seq_per_tile = p.packed ? (BLK / p.G) : BLK;  // sequence positions covered by one q tile
 
-  if (warp == kLoadWarp || warp == kLoadWarp + 1) {
-    // ======================================= TMA producers ======================================
-    // One producer warp per stream: each fills only its own stream's ring, so a full ring of one stream
-    // never holds back the loads of the other.  Producer 0 also loads the Q tiles.
-    setmaxnreg_dec<56>();
-    const int ls = warp - kLoadWarp;
-    uint32_t ring_cnt[2] = {0, 0};  // tiles produced so far into each stream's ring
-    uint32_t q_cnt = 0;
+  if (warp == kLoadWarp) {
+    // ======================================= TMA producer =======================================
+    setmaxnreg_dec<40>();
+    uint32_t ring_cnt = 0, q_cnt = 0;
     bool ok = true;
     PT_DECL
     for (int band = 0; band * (int)gridDim.x < p.num_work && ok; ++band) {
@@ -242,53 +223,22 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const int n_it = t.it_end - t.it_begin;
       if (n_it <= 0) continue;
       PT_MARK(0)
-      if (ls == 0) {
-        // Q tile
-        ok = mbar_wait(BAR(kQEmpty), (q_cnt & 1) ^ 1, wctx, 100);
-        if (!ok) break;
-        PT_MARK(1)
-        if (lane == 0) {
-          // a 64-row query tile fills only the top half of each slab
-          mbar_arrive_expect_tx(BAR(kQFull), Cfg::kSlabs * BLK * 128);
+      ok = mbar_wait(BAR(kQEmpty), (q_cnt & 1) ^ 1, wctx, 100);
+      if (!ok) break;
+      PT_MARK(1)
+      if (lane == 0) {
+        // a 64-row query tile fills only the top half of each slab
+        mbar_arrive_expect_tx(BAR(kQFull), Cfg::kSlabs * BLK * 128);
 #pragma unroll
-          for (int sl = 0; sl < Cfg::kSlabs; ++sl) {
-            tma_load_5d(smem_u32(sQ + sl * Cfg::kSlabBytes), &tm_q, BAR(kQFull), sl * (128 / Cfg::kElt),
-                        t.g, t.m * seq_per_tile, t.hkv, t.b);
-          }
+        for (int sl = 0; sl < Cfg::kSlabs; ++sl) {
+          tma_load_5d(smem_u32(sQ + sl * Cfg::kSlabBytes), &tm_q, BAR(kQFull), sl * (128 / Cfg::kElt), t.g,
+                      t.m * seq_per_tile, t.hkv, t.b);
         }
-        ++q_cnt;
       }
-
-      // K/V tiles of this producer's stream in its consumption order: K(s), V(s), K(s+2), V(s+2), ...
-      auto issue_tile = [&](const CUtensorMap* tm, int strm, int blk0, int blk1) -> bool {
-        const uint32_t depth = strm ? (uint32_t)(NS - Cfg::kRing0) : (uint32_t)Cfg::kRing0;
-        const uint32_t stage = (strm ? (uint32_t)Cfg::kRing0 : 0u) + ring_cnt[strm] % depth;
-        const uint32_t ph = (ring_cnt[strm] / depth) & 1;
-        PT_MARK(0)
-        if (!mbar_wait(BAR(kKvEmpty + stage), ph ^ 1, wctx, 101)) return false;
-        PT_MARK(2)
-        if (lane == 0) {
-          uint8_t* dst = sKV + stage * Cfg::kTileBytes;
-          mbar_arrive_expect_tx(BAR(kKvFull + stage), Cfg::kTileBytes);
-#pragma unroll
-          for (int sl = 0; sl < Cfg::kSlabs; ++sl) {
-            const int c0 = sl * (128 / Cfg::kElt);
-            if (BLK == 128) {
-              tma_load_4d(smem_u32(dst + sl * Cfg::kSlabBytes), tm, BAR(kKvFull + stage), c0,
-                          blk0 * 128, t.hkv, t.b);
-            } else {
-              tma_load_4d(smem_u32(dst + sl * Cfg::kSlabBytes), tm, BAR(kKvFull + stage), c0,
-                          blk0 * 64, t.hkv, t.b);
-              tma_load_4d(smem_u32(dst + sl * Cfg::kSlabBytes + 64 * 128), tm, BAR(kKvFull + stage),
-                          c0, blk1 * 64, t.hkv, t.b);
-            }
-          }
-        }
-        ++ring_cnt[strm];
-        return true;
-      };
-      // block ids of KV iteration `it` (relative to the row start)
-      auto fetch = [&](int it, int& j0, int& j1) {
+      ++q_cnt;
+      for (int i = 0; i < n_it && ok; ++i) {
+        const int it = t.it_begin + i;
+        int j0, j1;
         if (BLK == 128) {
           j0 = t.row[it];
           j1 = j0;
@@ -296,28 +246,40 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           j0 = t.row[2 * it];
           j1 = (2 * it + 1 < t.count) ? t.row[2 * it + 1] : j0;
         }
-      };
-      for (int i = ls; i < n_it && ok; i += 2) {
-        int j0, j1;
-        fetch(t.it_begin + i, j0, j1);
-        ok = issue_tile(&tm_k, ls, j0, j1);
-        if (ok) ok = issue_tile(&tm_v, ls, j0, j1);
+#pragma unroll
+        for (int which = 0; which < 2; ++which) {  // K(i), then V(i)
+          const CUtensorMap* tm = which ? &tm_v : &tm_k;
+          const uint32_t stage = ring_cnt % NS;
+          PT_MARK(0)
+          ok = mbar_wait(BAR(kKvEmpty + stage), ((ring_cnt / NS) & 1) ^ 1, wctx, 101);
+          if (!ok) break;
+          PT_MARK(2)
+          if (lane == 0) {
+            uint8_t* dst = sKV + stage * Cfg::kTileBytes;
+            mbar_arrive_expect_tx(BAR(kKvFull + stage), Cfg::kTileBytes);
+#pragma unroll
+            for (int sl = 0; sl < Cfg::kSlabs; ++sl) {
+              const int c0 = sl * (128 / Cfg::kElt);
+              if (BLK == 128) {
+                tma_load_4d(smem_u32(dst + sl * Cfg::kSlabBytes), tm, BAR(kKvFull + stage), c0, j0 * 128, t.hkv, t.b);
+              } else {
+                tma_load_4d(smem_u32(dst + sl * Cfg::kSlabBytes), tm, BAR(kKvFull + stage), c0, j0 * 64, t.hkv, t.b);
+                tma_load_4d(smem_u32(dst + sl * Cfg::kSlabBytes + 64 * 128), tm, BAR(kKvFull + stage), c0, j1 * 64,
+                            t.hkv, t.b);
+              }
+            }
+          }
+          ++ring_cnt;
+        }
       }
     }
     PT_FLUSH(48)
-  } else if (warp == kMmaWarp || warp == kMmaWarp + 1) {
+  } else if (warp == kMmaWarp) {
     // ========================================= MMA issue ========================================
-    // One issuing warp per stream.  tcgen05.mma issue stalls the issuing thread at the execution rate,
-    // so with a single issuer the tensor pipe idles during every barrier wait and commit; with two
-    // issuers one stream's bookkeeping overlaps the other stream's MMAs.  Per stream the order
-    // PV(i) -> QK(i+2) is program order of one thread, which is what the aliasing of P_s with S_s needs.
-    // The two issuers take turns: QK(0), QK(1), {PV(0),QK(2)}, {PV(1),QK(3)}, ... enter the tensor pipe
-    // as whole batches in iteration order.  Left to themselves the streams lock in phase (both in their
-    // softmax, then both in their MMAs, measured); batches handed over by a token keep them half a
-    // cycle apart, so one stream's softmax runs under the other stream's MMAs.
-    setmaxnreg_dec<56>();
-    const int s = warp - kMmaWarp;
-    const uint32_t tS_s = tmem + 128u * (uint32_t)s, tO_s = tmem + 256u + 128u * (uint32_t)s;
+    // Order inside a tile: QK(0), {PV(0), QK(1)}, {PV(1), QK(2)}, ...: S(i+1) overwrites the tensor-memory
+    // columns P(i) lives in, so it follows PV(i) in this thread's program order.  While this CTA's softmax works on
+    // S(i), the tensor pipe belongs to the CTA that shares the SM.
+    setmaxnreg_dec<40>();
     const uint32_t kFmt = (FP8 || p.f16) ? 0u : 1u;  // e4m3 (kind::f8f6f4) or f16 (kind::f16) = 0, bf16 = 1
     const uint32_t idesc_qk = umma_idesc(kFmt, kFmt, 0, 0, 128, 128);
     // Narrower heads (D = 64 or 96, 16-bit inputs only) use the head's own tile shape: QK^T contracts over D / 16
@@ -325,24 +287,12 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     // PV produces D output columns.
     const uint32_t idesc_pv = umma_idesc(kFmt, kFmt, 0, 1, 128, (uint32_t)p.D);
     const int qk_steps = FP8 ? Cfg::kKSteps : p.D / 16;
-    uint32_t ring_pos = 0, q_cnt = 0, p_cnt = 0;  // ring_pos: tiles of this stream's ring consumed so far
-    const uint32_t ring_depth = s ? (uint32_t)(NS - Cfg::kRing0) : (uint32_t)Cfg::kRing0;
-    const uint32_t ring_first = s ? (uint32_t)Cfg::kRing0 : 0u;
-    bool ok = true;
-    uint32_t turn_cnt = 0;      // completed waits on this issuer's turn barrier
-    auto turn_wait = [&]() -> bool {
-      const bool r = mbar_wait(turn_base + 8u * s, turn_cnt & 1, wctx, 205);
-      ++turn_cnt;
-      return r;
-    };
-    auto turn_pass = [&]() {
-      if (lane == 0) mbar_arrive(turn_base + 8u * (s ^ 1));
-      __syncwarp();
-    };
-    // descriptors are built once; a byte offset b inside a tile is an addition of b >> 4 to the low word
+    const uint32_t led = lane == 0;
+    uint32_t ring_pos = 0, q_cnt = 0, p_cnt = 0;
     const uint64_t q_desc = umma_desc_sw128(smem_u32(sQ), 0, 1024);
-    const uint64_t k_desc0 = umma_desc_sw128(smem_u32(sKV), 0, 1024);                               // K-major view
+    const uint64_t k_desc0 = umma_desc_sw128(smem_u32(sKV), 0, 1024);                                      // K-major view
     const uint64_t v_desc0 = umma_desc_sw128(smem_u32(sKV), FP8 ? 0u : (uint32_t)Cfg::kSlabBytes, 1024);  // MN-major
+    bool ok = true;
     PT_DECL
     for (int band = 0; band * (int)gridDim.x < p.num_work && ok; ++band) {
       const int w = snake_work(band);
@@ -355,41 +305,35 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       if (!ok) break;
       PT_MARK(1)
       ++q_cnt;
-      // this stream's ring holds K(s), V(s), K(s+2), V(s+2), ... and is consumed in exactly that order
-      auto issue_qk = [&](int i, bool take_turn) -> bool {
-        const uint32_t stage = ring_first + ring_pos % ring_depth;
+      auto issue_qk = [&](bool last) -> bool {
+        const uint32_t stage = ring_pos % NS;
         PT_MARK(0)
-        if (!mbar_wait(BAR(kKvFull + stage), (ring_pos / ring_depth) & 1, wctx, 201)) return false;
+        if (!mbar_wait(BAR(kKvFull + stage), (ring_pos / NS) & 1, wctx, 201)) return false;
         ++ring_pos;
         PT_MARK(2)
-        if (take_turn && !turn_wait()) return false;
-        PT_MARK(5)
-        PT_MARK(0)
-        {
-          const uint32_t led = lane == 0;
-          const uint64_t kd = k_desc0 + (uint64_t)stage * (Cfg::kTileBytes >> 4);
+        tc_fence_after();
+        const uint64_t kd = k_desc0 + (uint64_t)stage * (Cfg::kTileBytes >> 4);
 #pragma unroll
-          for (int k = 0; k < Cfg::kKSteps; ++k) {
-            const uint64_t off = FP8 ? (uint64_t)(k * 2) : (uint64_t)((k >> 2) * (Cfg::kSlabBytes >> 4) + (k & 3) * 2);
-            if (FP8) umma_f8_ss_led(tS_s, q_desc + off, kd + off, idesc_qk, k > 0, led);
-            else umma_f16_ss_led(tS_s, q_desc + off, kd + off, idesc_qk, k > 0, (k < qk_steps) ? led : 0u);
-          }
-          umma_commit_led(BAR(kSFull + s), led);
-          umma_commit_led(BAR(kKvEmpty + stage), led);
+        for (int k = 0; k < Cfg::kKSteps; ++k) {
+          const uint64_t off = FP8 ? (uint64_t)(k * 2) : (uint64_t)((k >> 2) * (Cfg::kSlabBytes >> 4) + (k & 3) * 2);
+          if (FP8) umma_f8_ss_led(tS, q_desc + off, kd + off, idesc_qk, k > 0, led);
+          else umma_f16_ss_led(tS, q_desc + off, kd + off, idesc_qk, k > 0, (k < qk_steps) ? led : 0u);
         }
+        umma_commit_led(BAR(kSFull), led);
+        umma_commit_led(BAR(kKvEmpty + stage), led);
+        if (last) umma_commit_led(BAR(kQEmpty), led);  // the tile's last S: Q may be replaced
+        __syncwarp();
         PT_MARK(7)
         return true;
       };
-      auto issue_pv = [&](int i, bool take_turn) -> bool {
-        const uint32_t stage = ring_first + ring_pos % ring_depth;
+      auto issue_pv = [&](int i, bool last) -> bool {
+        const uint32_t stage = ring_pos % NS;
         PT_MARK(0)
-        if (!mbar_wait(BAR(kKvFull + stage), (ring_pos / ring_depth) & 1, wctx, 202)) return false;
+        if (!mbar_wait(BAR(kKvFull + stage), (ring_pos / NS) & 1, wctx, 202)) return false;
         ++ring_pos;
         PT_MARK(3)
-        if (!mbar_wait(BAR(kPHalf + s), p_cnt & 1, wctx, 203)) return false;  // first half of P_s
+        if (!mbar_wait(BAR(kPHalf), p_cnt & 1, wctx, 203)) return false;  // first half of P
         PT_MARK(4)
-        if (take_turn && !turn_wait()) return false;
-        PT_MARK(5)
         tc_fence_after();
         const uint64_t vd = v_desc0 + (uint64_t)stage * (Cfg::kTileBytes >> 4);
         auto pv_steps = [&](int k0, int k1) {
@@ -398,70 +342,40 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             // V is MN-major: one k step = kMmaK token rows of 128 B; the second 64-channel slab of a
             // bf16 tile is reached through the leading byte offset.
             const uint64_t db = vd + (uint64_t)(k * ((Cfg::kMmaK * 128) >> 4));
-            const uint32_t a_t = tS_s + (uint32_t)k * Cfg::kPColsPerStep;
-            if (FP8) umma_f8_ts_led(tO_s, a_t, db, idesc_pv, (i >= 2) || (k > 0), lane == 0);
-            else umma_f16_ts_led(tO_s, a_t, db, idesc_pv, (i >= 2) || (k > 0), lane == 0);
+            const uint32_t a_t = tS + (uint32_t)k * Cfg::kPColsPerStep;
+            if (FP8) umma_f8_ts_led(tO, a_t, db, idesc_pv, (i > 0) || (k > 0), led);
+            else umma_f16_ts_led(tO, a_t, db, idesc_pv, (i > 0) || (k > 0), led);
           }
         };
-        PT_MARK(0)
         pv_steps(0, Cfg::kKSteps / 2);
         PT_MARK(6)
-        PT_MARK(0)
-        if (!mbar_wait(BAR(kPFull + s), p_cnt & 1, wctx, 204)) return false;  // second half
+        if (!mbar_wait(BAR(kPFull), p_cnt & 1, wctx, 204)) return false;  // second half
         PT_MARK(4)
         ++p_cnt;
         tc_fence_after();
-        PT_MARK(0)
         pv_steps(Cfg::kKSteps / 2, Cfg::kKSteps);
-        umma_commit_led(BAR(kKvEmpty + stage), lane == 0);
+        umma_commit_led(BAR(kKvEmpty + stage), led);
+        if (last) umma_commit_led(BAR(kOFinal), led);
+        __syncwarp();
         PT_MARK(6)
         return true;
       };
-
-      // turns of this tile: QK(0) [stream 0], QK(1) [stream 1], then batch i = {PV(i), QK(i+2)} by stream
-      // i & 1.  Every turn but the first waits for the token of its predecessor and every turn but the last
-      // passes it on, so all passes are consumed inside the tile (tiles are ordered among themselves by the
-      // Q buffer: the next Q tile is loaded only after both issuers have finished this one).  Short rows
-      // are not worth the hand-offs: below kTurnMinIters iterations the issuers run freely.
-      constexpr int kTurnMinIters = 6;
-      const bool turns = n_it >= kTurnMinIters;
-      if (s == 0) {
-        ok = issue_qk(0, false);
-        if (ok && turns) turn_pass();
-      } else if (n_it >= 2) {
-        ok = issue_qk(1, turns);
-        if (ok && turns) turn_pass();
+      ok = issue_qk(n_it == 1);
+      for (int i = 0; i < n_it && ok; ++i) {
+        ok = issue_pv(i, i == n_it - 1);
+        if (ok && i + 1 < n_it) ok = issue_qk(i + 2 == n_it);
       }
-      for (int i = s; i < n_it && ok; i += 2) {
-        ok = issue_pv(i, turns);
-        if (ok && i + 2 < n_it) ok = issue_qk(i + 2, false);
-        if (ok && turns && i + 1 < n_it) turn_pass();
-      }
-      if (!ok) break;
-      // Q is free once the QK MMAs of BOTH streams have completed: each issuer signals for its own MMAs
-      // (a stream without work arrives directly; it cannot arrive twice in one phase because the next Q
-      // tile, which it waits for first, is only loaded after this phase has completed).  O_s is final
-      // when stream s's own PV MMAs have completed.
-      if (lane == 0) {
-        if (s < n_it) {
-          umma_commit(BAR(kQEmpty));
-          umma_commit(BAR(kOFinal + s));
-        } else {
-          mbar_arrive(BAR(kQEmpty));
-        }
-      }
-      __syncwarp();
     }
     PT_MARK(0)
-    if (s == 0) { PT_FLUSH(32) } else { PT_FLUSH(40) }
-  } else if (warp < 8) {
+    PT_FLUSH(32)
+  } else if (warp < 4) {
     // ===================================== softmax + epilogue ===================================
+    // Four warps, one thread per query row (= tensor-memory lane), all 128 score columns of the row.
     setmaxnreg_inc<216>();
-    const int grp = warp >> 2;                 // stream owned by this group
-    const int row = threadIdx.x & 127;         // query row inside the tile = tensor-memory lane
-    const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
+    const int row = threadIdx.x;
+    const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
     const bool row_active = (BLK == 128) || (row < 64);  // warp-uniform
-    uint32_t s_cnt = 0, of_cnt[2] = {0, 0}, epi_a = 0, grp_b = 0;
+    uint32_t s_cnt = 0, of_cnt = 0;
     bool ok = true;
     const bool need_mask_meta = (p.block_sizes != nullptr) || (p.Sk % BLK != 0);
     constexpr float kRescaleThreshold = FP8 ? 1.8073549f /* log2(448/128) */ : 8.0f;
@@ -491,7 +405,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         q_row_scale = row_valid ? p.q_scale[((long long)t.b * p.Hq + hq) * p.Sq + seq] : 0.f;
       }
 
-      for (int i = grp; i < n_it && ok; i += 2) {
+      for (int i = 0; i < n_it && ok; ++i) {
         // mask metadata for this KV iteration
         int len0 = BLK, len1 = BLK;
         int j0 = 0;
@@ -526,7 +440,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         }
 
         PT_MARK(0)
-        ok = mbar_wait(BAR(kSFull + grp), s_cnt & 1, wctx, 300 + grp);
+        ok = mbar_wait(BAR(kSFull), s_cnt & 1, wctx, 300);
         if (!ok) break;
         PT_MARK(1)
         ++s_cnt;
@@ -534,13 +448,13 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (!row_active) {
           // idle half of a 64-row tile: only the barrier protocol
           tc_fence_before();
-          mbar_arrive(BAR(kPHalf + grp));
-          mbar_arrive(BAR(kPFull + grp));
+          mbar_arrive(BAR(kPHalf));
+          mbar_arrive(BAR(kPFull));
           continue;
         }
         float sv[128];
         uint32_t* su = reinterpret_cast<uint32_t*>(sv);
-        const uint32_t t_row = tS[grp] + lane_base;
+        const uint32_t t_row = tS + lane_base;
         const bool masked = (BLK == 128) ? (len0 < 128) : (len0 < 64 || len1 < 64);  // warp-uniform
         float bm;
         if (masked) {
@@ -635,7 +549,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           bm = fmaxf(m0, m1) * p.scale_log2;
         }
         const float m_new = fmaxf(m_cur, bm);
-        const bool first = (i == grp);
+        const bool first = (i == 0);
         if (first) {
           m_cur = m_new;
         } else {
@@ -644,16 +558,16 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             const float sc = (m_new == -INFINITY) ? 1.f : ex2_approx(m_cur - m_new);
             m_cur = m_new;
             l_sum *= sc;
-            // rescale O_s in tensor memory (the previous PV of this stream has completed: the commit
-            // that signalled S_s was issued after it)
+            // rescale O in tensor memory (the previous PV has completed: the commit that signalled this S
+            // was issued after it)
 #pragma unroll
             for (int c = 0; c < 4; ++c) {
               uint32_t o[32];
-              tmem_ld32(tO[grp] + lane_base + c * 32, o);
+              tmem_ld32(tO + lane_base + c * 32, o);
               tmem_wait_ld();
 #pragma unroll
               for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * sc);
-              tmem_st32(tO[grp] + lane_base + c * 32, o);
+              tmem_st32(tO + lane_base + c * 32, o);
             }
             tmem_wait_st();
           }
@@ -685,9 +599,9 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               if (c4 == 2) {
                 tmem_wait_st();
                 tc_fence_before();
-                mbar_arrive(BAR(kPHalf + grp));
+                mbar_arrive(BAR(kPHalf));
               }
-              tmem_st8(tS[grp] + lane_base + c4 * 8, pk);
+              tmem_st8(tS + lane_base + c4 * 8, pk);
             }
           } else {
             // The probabilities are rounded to e4m3 (three mantissa bits), so the exponentials are taken in
@@ -721,12 +635,12 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               unpack_f16x2(hadd2(hadd2(hs[0], hs[1]), hadd2(hs[2], hs[3])), lo, hi);
               if (c4 & 1) { a2 += lo; a3 += hi; } else { a0 += lo; a1 += hi; }
               if (c4 == 2) {
-                // first half of P_s (two MMA k steps) released on its own barrier, its stores long landed
+                // first half of P (two MMA k steps) released on its own barrier, its stores long landed
                 tmem_wait_st();
                 tc_fence_before();
-                mbar_arrive(BAR(kPHalf + grp));
+                mbar_arrive(BAR(kPHalf));
               }
-              tmem_st8(tS[grp] + lane_base + c4 * 8, pk);
+              tmem_st8(tS + lane_base + c4 * 8, pk);
             }
           }
         } else {
@@ -750,13 +664,13 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
               pk[e] = decltype(is_f16)::value ? pack_f16x2(x0, x1) : pack_bf16x2(x0, x1);
             }
             if (c4 == 2) {
-              // the first half of P_s (four MMA k steps) is released on its own barrier; waiting for its
+              // the first half of P (four MMA k steps) is released on its own barrier; waiting for its
               // stores only now, after the third chunk's arithmetic, keeps their latency off the path
               tmem_wait_st();
               tc_fence_before();
-              mbar_arrive(BAR(kPHalf + grp));
+              mbar_arrive(BAR(kPHalf));
             }
-            tmem_st16(tS[grp] + lane_base + c4 * 16, pk);
+            tmem_st16(tS + lane_base + c4 * 16, pk);
           }
           float y0, y1, y2, y3;
           unpack2(s0, y0, y1);
@@ -770,126 +684,91 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         PT_MARK(4)
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(BAR(kPFull + grp));
+        mbar_arrive(BAR(kPFull));
         PT_MARK(5)
       }
       if (!ok) break;
 
       // ------------------------------------ tile epilogue ------------------------------------
       PT_MARK(0)
-      // The (max, sum) pairs of the two streams are exchanged while the last PV MMAs are still running.
-      // The same rendezvous orders this tile's staging writes after the previous tile's output store.
-      s_stats[grp][row] = make_float2(m_cur, l_sum);
-      if (!SPLIT && (threadIdx.x & 127) == 0) tma_store_wait_read<0>();
-      ok = mbar_rendezvous_poll(BAR(kEpiA), epi_a, wctx, 320);
-      if (!ok) break;
-      const float2 st0 = s_stats[0][row];
-      const float2 st1 = s_stats[1][row];
-      const float m_all = fmaxf(st0.x, st1.x);
-      const float w0 = (st0.x == -INFINITY) ? 0.f : ex2_approx(st0.x - m_all);
-      const float w1 = (st1.x == -INFINITY) ? 0.f : ex2_approx(st1.x - m_all);
-      const float denom = st0.y * w0 + st1.y * w1;
-      const float inv = (denom > 0.f) ? (1.f / denom) : 0.f;
-      const float f0 = w0 * inv, f1 = w1 * inv;
-      const bool has0 = n_it > 0, has1 = n_it > 1;
+      const float inv = (l_sum > 0.f) ? (1.f / l_sum) : 0.f;
+      const float lse_log2 = (l_sum > 0.f) ? (m_cur + lg2_approx(l_sum) - kPBias) : -INFINITY;
       if (n_it > 0) {
-        ok = mbar_wait(BAR(kOFinal), of_cnt[0] & 1, wctx, 310 + grp);
+        ok = mbar_wait(BAR(kOFinal), of_cnt & 1, wctx, 310);
         if (!ok) break;
-        ++of_cnt[0];
-        if (n_it > 1) {
-          ok = mbar_wait(BAR(kOFinal + 1), of_cnt[1] & 1, wctx, 312 + grp);
-          if (!ok) break;
-          ++of_cnt[1];
-        }
+        ++of_cnt;
         tc_fence_after();
       }
       PT_MARK(6)
-
-      // this group finalises output columns [64*grp, 64*grp+64)
-      float acc[64];
-#pragma unroll
-      for (int e = 0; e < 64; ++e) acc[e] = 0.f;
-      if (row_active) {
-        if (has0) {
-          uint32_t o[64];
-          tmem_ld32(tO[0] + lane_base + grp * 64, o);
-          tmem_ld32(tO[0] + lane_base + grp * 64 + 32, o + 32);
-          tmem_wait_ld();
-#pragma unroll
-          for (int e = 0; e < 64; ++e) acc[e] = __uint_as_float(o[e]) * f0;
-        }
-        if (has1) {
-          uint32_t o[64];
-          tmem_ld32(tO[1] + lane_base + grp * 64, o);
-          tmem_ld32(tO[1] + lane_base + grp * 64 + 32, o + 32);
-          tmem_wait_ld();
-#pragma unroll
-          for (int e = 0; e < 64; ++e) acc[e] = fmaf(__uint_as_float(o[e]), f1, acc[e]);
-        }
-      }
-      tc_fence_before();
-
-      if (FP8) {
-        const float* vs = p.v_scale + (long long)hq * 128 + grp * 64;
-#pragma unroll
-        for (int e = 0; e < 64; ++e) acc[e] *= vs[e];
-      }
-      const float lse_log2 = (denom > 0.f) ? (m_all + lg2_approx(denom) - kPBias) : -INFINITY;
-
+      // Every thread finalises its own row, 32 columns at a time, straight from tensor memory to global memory
+      // (a row is 256 contiguous bytes).  The next tile's first PV overwrites O only after P(0) of that tile, which
+      // these same threads write after this loop.
+      const float* vs = FP8 ? p.v_scale + (long long)hq * 128 : nullptr;
+      long long prow = 0;
+      float4* dst_f = nullptr;
+      uint4* dst_h = nullptr;
       if (SPLIT) {
-        if (row_valid) {
-          const long long prow = (((long long)t.split * p.B + t.b) * p.Hq + hq) * p.Sq + seq;
-          float4* dst = reinterpret_cast<float4*>(p.partial_o + prow * 128 + grp * 64);
-#pragma unroll
-          for (int e = 0; e < 16; ++e)
-            dst[e] = make_float4(acc[4 * e], acc[4 * e + 1], acc[4 * e + 2], acc[4 * e + 3]);
-          if (grp == 0) p.partial_lse[prow] = lse_log2 * kLn2;
-        }
-        // every thread has read its share of O0 / O1: the next tile may overwrite them
-        ok = mbar_rendezvous_poll(BAR(kGrpB), grp_b, wctx, 323);
-        if (!ok) break;
+        prow = (((long long)t.split * p.B + t.b) * p.Hq + hq) * p.Sq + seq;
+        dst_f = reinterpret_cast<float4*>(p.partial_o + prow * 128);
       } else {
-        // stage bf16 in shared memory in the 128-byte-swizzled layout the output tensor map expects
-        const bool issuer = (threadIdx.x & 127) == 0;
-        if (row_active) {
-          uint8_t* slab = sO + grp * (128 * 128);
+        dst_h = reinterpret_cast<uint4*>(p.out + (long long)t.b * p.o_stride_b + (long long)hq * p.o_stride_h +
+                                         (long long)seq * p.o_stride_s);
+      }
 #pragma unroll
-          for (int ch = 0; ch < 8; ++ch) {
-            uint4 v;
-            if (p.f16) {
-              v.x = pack_f16x2(acc[ch * 8 + 0], acc[ch * 8 + 1]);
-              v.y = pack_f16x2(acc[ch * 8 + 2], acc[ch * 8 + 3]);
-              v.z = pack_f16x2(acc[ch * 8 + 4], acc[ch * 8 + 5]);
-              v.w = pack_f16x2(acc[ch * 8 + 6], acc[ch * 8 + 7]);
-            } else {
-              v.x = pack_bf16x2(acc[ch * 8 + 0], acc[ch * 8 + 1]);
-              v.y = pack_bf16x2(acc[ch * 8 + 2], acc[ch * 8 + 3]);
-              v.z = pack_bf16x2(acc[ch * 8 + 4], acc[ch * 8 + 5]);
-              v.w = pack_bf16x2(acc[ch * 8 + 6], acc[ch * 8 + 7]);
+      for (int c = 0; c < 4; ++c) {
+        float acc[32];
+        if (row_active && n_it > 0) {
+          uint32_t o[32];
+          tmem_ld32(tO + lane_base + c * 32, o);
+          tmem_wait_ld();
+#pragma unroll
+          for (int e = 0; e < 32; ++e) acc[e] = __uint_as_float(o[e]) * inv;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) acc[e] = 0.f;
+        }
+        if (FP8) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) acc[e] *= vs[c * 32 + e];
+        }
+        if (row_valid) {
+        if (SPLIT) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e)
+            dst_f[c * 8 + e] = make_float4(acc[4 * e], acc[4 * e + 1], acc[4 * e + 2], acc[4 * e + 3]);
+        } else {
+#pragma unroll
+          for (int ch = 0; ch < 4; ++ch) {
+            if (c * 32 + ch * 8 < p.D) {  // narrower heads: the columns beyond D do not exist
+              uint4 v;
+              if (p.f16) {
+                v.x = pack_f16x2(acc[ch * 8 + 0], acc[ch * 8 + 1]);
+                v.y = pack_f16x2(acc[ch * 8 + 2], acc[ch * 8 + 3]);
+                v.z = pack_f16x2(acc[ch * 8 + 4], acc[ch * 8 + 5]);
+                v.w = pack_f16x2(acc[ch * 8 + 6], acc[ch * 8 + 7]);
+              } else {
+                v.x = pack_bf16x2(acc[ch * 8 + 0], acc[ch * 8 + 1]);
+                v.y = pack_bf16x2(acc[ch * 8 + 2], acc[ch * 8 + 3]);
+                v.z = pack_bf16x2(acc[ch * 8 + 4], acc[ch * 8 + 5]);
+                v.w = pack_bf16x2(acc[ch * 8 + 6], acc[ch * 8 + 7]);
+              }
+              dst_h[c * 4 + ch] = v;
             }
-            *reinterpret_cast<uint4*>(slab + row * 128 + ((ch ^ (row & 7)) << 4)) = v;
           }
         }
-        fence_proxy_async_smem();
-        // both groups: the staging tile is complete, and every thread has read its share of O0 / O1, so the
-        // next tile may overwrite them
-        ok = mbar_rendezvous_poll(BAR(kGrpB), grp_b, wctx, 323);
-        if (!ok) break;
-        if (issuer && grp * 64 < p.D) {  // a 64-wide head has no second column slab to store
-          const int cs = t.m * seq_per_tile;
-          tma_store_5d(&tm_o, smem_u32(sO + grp * (128 * 128)), grp * 64, t.g, cs, t.hkv, t.b);
-          tma_store_commit();
         }
-        if (grp == 0 && row_valid && p.lse != nullptr) {
-          p.lse[((long long)t.b * p.Hq + hq) * p.Sq + seq] = lse_log2 * kLn2;
-        }
+        __syncwarp();
+      }
+      tc_fence_before();
+      if (row_valid) {
+        if (SPLIT) p.partial_lse[prow] = lse_log2 * kLn2;
+        else if (p.lse != nullptr) p.lse[((long long)t.b * p.Hq + hq) * p.Sq + seq] = lse_log2 * kLn2;
       }
       PT_MARK(7)
     }
-    if ((threadIdx.x & 127) == 0 && !SPLIT) tma_store_wait_all<0>();
-    if ((warp & 3) == 0) { PT_FLUSH(grp * 8) }
+    if (warp == 0) { PT_FLUSH(0) }
   } else {
-    setmaxnreg_dec<56>();
+    setmaxnreg_dec<40>();
   }
 
   // ------------------------------------------ teardown ------------------------------------------
@@ -897,7 +776,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   __syncthreads();
   if (warp == kMmaWarp) {
     tc_fence_after();
-    tmem_dealloc(tmem, 512);
+    tmem_dealloc(tmem, 256);
   }
 }
 
@@ -907,7 +786,7 @@ bsa_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 
 template <int BLK, bool FP8, bool SPLIT>
 static int launch_fwd(const bsa_fwd_args& a, const FwdParams& p, const CUtensorMap& tq,
-                      const CUtensorMap& tk, const CUtensorMap& tv, const CUtensorMap& to,
+                      const CUtensorMap& tk, const CUtensorMap& tv,
                       int num_sms, cudaStream_t stream) {
   using Cfg = FwdCfg<FP8>;
   auto kern = bsa_fwd_kernel<BLK, FP8, SPLIT>;
@@ -916,9 +795,9 @@ static int launch_fwd(const bsa_fwd_args& a, const FwdParams& p, const CUtensorM
                                          Cfg::kSmemBytes);
     if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "cudaFuncSetAttribute(smem): %s", cudaGetErrorString(e));
   }
-  const int grid = p.num_work < num_sms ? p.num_work : num_sms;
+  const int grid = p.num_work < kCtasPerSm * num_sms ? p.num_work : kCtasPerSm * num_sms;
   if (grid <= 0) return BSA_OK;
-  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, to, p);
+  kern<<<grid, kThreads, Cfg::kSmemBytes, stream>>>(tq, tk, tv, p);
   cudaError_t e = cudaGetLastError();
   if (e != cudaSuccess) return set_error(BSA_ERR_CUDA, "forward launch: %s", cudaGetErrorString(e));
   (void)a;
@@ -988,6 +867,10 @@ extern "C" int bsa_fwd(const bsa_fwd_args* a, void* cuda_stream) {
   p.q_scale = a->q_scale;
   p.k_scale = a->k_scale;
   p.v_scale = a->v_scale;
+  p.out = static_cast<uint8_t*>(a->out);
+  p.o_stride_b = (long long)a->o_stride[0] * 2;
+  p.o_stride_h = (long long)a->o_stride[1] * 2;
+  p.o_stride_s = (long long)a->o_stride[2] * 2;
   p.lse = a->lse;
   p.partial_o = a->partial_o;
   p.partial_lse = a->partial_lse;
@@ -1021,7 +904,7 @@ extern "C" int bsa_fwd(const bsa_fwd_args* a, void* cuda_stream) {
   const CUtensorMapDataType dt16 = a->dtype == BSA_DTYPE_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const CUtensorMapDataType dt = fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : dt16;
   const uint32_t inner = 128 / elt;  // elements per 128-byte swizzle row
-  CUtensorMap tq, tk, tv, to;
+  CUtensorMap tq, tk, tv;
   {
     // the innermost extent is the true head dimension: boxes that reach beyond it read zeros / are clipped
     uint64_t dims[5] = {(uint64_t)a->D, (uint64_t)G, (uint64_t)a->Sq, (uint64_t)a->Hkv, (uint64_t)a->B};
@@ -1030,15 +913,6 @@ extern "C" int bsa_fwd(const bsa_fwd_args* a, void* cuda_stream) {
     uint32_t box[5] = {inner, packed ? (uint32_t)G : 1u, (uint32_t)(packed ? a->blk / G : a->blk), 1, 1};
     int rc = make_tensor_map(&tq, dt, 5, a->q, dims, str, box, "q");
     if (rc) return rc;
-    if (a->splits == 1) {
-      uint64_t ostr[4] = {(uint64_t)a->o_stride[1] * 2, (uint64_t)a->o_stride[2] * 2,
-                          (uint64_t)a->o_stride[1] * G * 2, (uint64_t)a->o_stride[0] * 2};
-      uint32_t obox[5] = {64, packed ? (uint32_t)G : 1u, (uint32_t)(packed ? a->blk / G : a->blk), 1, 1};
-      rc = make_tensor_map(&to, dt16, 5, a->out, dims, ostr, obox, "out");
-      if (rc) return rc;
-    } else {
-      to = tq;
-    }
   }
   {
     uint64_t dims[4] = {(uint64_t)a->D, (uint64_t)a->Sk, (uint64_t)a->Hkv, (uint64_t)a->B};
@@ -1057,15 +931,15 @@ extern "C" int bsa_fwd(const bsa_fwd_args* a, void* cuda_stream) {
   const bool split = a->splits > 1;
   if (fp8) {
     if (a->blk == 128)
-      return split ? launch_fwd<128, true, true>(*a, p, tq, tk, tv, to, num_sms, stream)
-                   : launch_fwd<128, true, false>(*a, p, tq, tk, tv, to, num_sms, stream);
-    return split ? launch_fwd<64, true, true>(*a, p, tq, tk, tv, to, num_sms, stream)
-                 : launch_fwd<64, true, false>(*a, p, tq, tk, tv, to, num_sms, stream);
+      return split ? launch_fwd<128, true, true>(*a, p, tq, tk, tv, num_sms, stream)
+                   : launch_fwd<128, true, false>(*a, p, tq, tk, tv, num_sms, stream);
+    return split ? launch_fwd<64, true, true>(*a, p, tq, tk, tv, num_sms, stream)
+                 : launch_fwd<64, true, false>(*a, p, tq, tk, tv, num_sms, stream);
   }
   if (a->blk == 128) {
-    return split ? launch_fwd<128, false, true>(*a, p, tq, tk, tv, to, num_sms, stream)
-                 : launch_fwd<128, false, false>(*a, p, tq, tk, tv, to, num_sms, stream);
+    return split ? launch_fwd<128, false, true>(*a, p, tq, tk, tv, num_sms, stream)
+                 : launch_fwd<128, false, false>(*a, p, tq, tk, tv, num_sms, stream);
   }
-  return split ? launch_fwd<64, false, true>(*a, p, tq, tk, tv, to, num_sms, stream)
-               : launch_fwd<64, false, false>(*a, p, tq, tk, tv, to, num_sms, stream);
+  return split ? launch_fwd<64, false, true>(*a, p, tq, tk, tv, num_sms, stream)
+               : launch_fwd<64, false, false>(*a, p, tq, tk, tv, num_sms, stream);
 }

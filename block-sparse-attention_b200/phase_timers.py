@@ -7,7 +7,8 @@
 Loads the instrumented library (``libbsa_b200_timers.so``: lane 0 of one warp per role accumulates
 ``clock64()`` deltas per phase, summed over all CTAs), runs the forward and the backward of the workload
 a few times and prints, for every role, the clocks per active (q block, kv block) pair of one CTA.  All
-rows of one kernel add up to about the same total: the kernel's clocks per pair.  The numbers are taken
+rows of one kernel add up to about the same total: the kernel's clocks per pair of one CTA (the forward runs
+two CTAs per SM, so an SM spends half of that per pair).  The numbers are taken
 with the timers compiled in, which costs a few percent; they locate waits, they are not bench values.
 """
 from __future__ import annotations
@@ -19,13 +20,11 @@ import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 
-FWD_ROLES = {
-    "softmax group 0": 0, "softmax group 1": 8, "MMA issuer 0": 32, "MMA issuer 1": 40, "TMA producers (sum)": 48,
-}
+FWD_ROLES = {"softmax warps": 0, "MMA issuer": 32, "TMA producer": 48}
 FWD_PHASES = {
     "softmax": ["other", "wait S", "tmem ld + first max", "max + rescale", "exp + P store", "st wait + arrive",
-                "epilogue: stats + wait O", "epilogue: merge + store"],
-    "issuer": ["other", "wait Q", "wait K", "wait V", "wait P", "wait turn", "issue PV", "issue QK"],
+                "epilogue: wait O", "epilogue: scale + store"],
+    "issuer": ["other", "wait Q", "wait K", "wait V", "wait P", "-", "issue PV", "issue QK"],
     "producer": ["other", "wait Q free", "wait ring free", "-", "-", "-", "-", "-"],
 }
 BWD_ROLES = {

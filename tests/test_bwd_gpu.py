@@ -325,3 +325,20 @@ def test_host_pipeline_matches_direct_calls():
     dq, dk, dv = bsa_attn_bwd(doc, qc, kc, vc, out, lse, ic, 0, q2k_block_nums=nc, sparse_block_size=128)
     for name, ref in (("out", out), ("lse", lse), ("dq", dq), ("dk", dk), ("dv", dv)):
         assert torch.equal(host_out[name], ref.cpu()), name
+
+
+def test_backward_passes_launched_one_by_one_give_the_same_gradients():
+    """`stages` (a profiling knob of the C entry point): preprocess, dQ and dK/dV launched as three calls write
+    exactly what the single call writes."""
+    from block_sparse_attention import bsa_attn_bwd, bsa_attn_fwd
+    from block_sparse_attention.bsa_attn_interface import _bsa_attn_bwd
+    q, k, v, do, index, nums = _case(31, 1, 2, 1024, 1024, [3, 1, 4, 2], blk=128)
+    qc, kc, vc, doc, ic, nc = (t.cuda() for t in (q, k, v, do, index, nums))
+    out, lse = bsa_attn_fwd(qc, kc, vc, ic, 0, q2k_block_nums=nc, return_lse=True, sparse_block_size=128)
+    ref = bsa_attn_bwd(doc, qc, kc, vc, out, lse, ic, 0, q2k_block_nums=nc, sparse_block_size=128)
+    bufs = [torch.full_like(qc, 3.0) for _ in range(3)]
+    for mask in (1, 2, 4):
+        _bsa_attn_bwd(doc, qc, kc, vc, out, lse, ic, 0, q2k_block_nums=nc, dq=bufs[0], dk=bufs[1], dv=bufs[2],
+                      sparse_block_size=128, stages=mask)
+    for a, b in zip(ref, bufs):
+        assert torch.equal(a, b)

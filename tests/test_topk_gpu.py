@@ -40,6 +40,12 @@ def test_ties_nan_and_infinities():
     assert got[1].tolist() == [0, 1, 2]
     assert got[2].tolist() == [1, 2, 3]      # NaN ranks above +inf, like torch.topk
     assert torch.equal(got[:2], orc.topk_q2k(scores[:2], 3))
+    # a NaN with the sign bit set (the default quiet NaN of x86 arithmetic, 0xFFC00000) ranks the same way
+    scores = torch.tensor([[2.0, 0.0, float("inf"), 1.0, float("-inf")]])
+    scores.view(torch.int32)[0, 1] = 0xFFC00000 - (1 << 32)
+    assert torch.isnan(scores[0, 1])
+    assert topk_q2k(scores.cuda(), 2).cpu()[0].tolist() == [1, 2]
+    assert torch.topk(scores, 2).indices.sort().values[0].tolist() == [1, 2]
 
 
 def test_block_mean_and_scores_and_end_to_end_index():
