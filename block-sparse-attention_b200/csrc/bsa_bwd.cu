@@ -692,6 +692,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   if (warp == kDkvLoadWarp) {
     uint32_t r_cnt = 0, kv_cnt = 0, tile_cnt = 0;
     bool ok = true;
+    PT_DECL
     for (int band = 0; band * (int)gridDim.x < num_work && ok; ++band) {
       const int w = bwd_work_at(p.order_kv, band, num_work, p.status);
       if (w < 0) continue;
@@ -699,7 +700,9 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       const int bh = w / p.Nkv;
       const int h = bh % p.H, b = bh / p.H;
       if (total_rows(bh, nb) == 0) continue;
+      PT_MARK(0)
       ok = mbar_wait(BAR(kKvEmpty), (kv_cnt & 1) ^ 1, wctx, 500);
+      PT_MARK(1)
       if (!ok) break;
       ++kv_cnt;
       if (lane == 0) {
@@ -713,7 +716,9 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       auto load_pair = [&](int qa, int qb) -> bool {
         for (int which = 0; which < 2; ++which) {
           const uint32_t stage = r_cnt % NS, ph = (r_cnt / NS) & 1;
+          PT_MARK(0)
           if (!mbar_wait(BAR(kREmpty + stage), ph ^ 1, wctx, 501)) return false;
+          if (which) { PT_MARK(3) } else { PT_MARK(2) }
           if (lane == 0) {
             const CUtensorMap* tm = which ? &tm_do : &tm_q;
             mbar_arrive_expect_tx(BAR(kRFull + stage), kTile + (which ? 1024 : 0));
@@ -761,6 +766,8 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       }
       if (ok && pending >= 0) ok = load_pair(pending, pending);  // odd total: masked phantom second half
     }
+    PT_MARK(0)
+    PTB_FLUSH(64 + 32)
   } else if (warp == kBwdMmaWarp || warp == kBwdMmaWarp + 1) {
     // Two issuing warps.  The tensor pipe executes MMAs in the order they were issued, whoever issued them, so the
     // order decides what arrives late:
@@ -796,7 +803,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
       auto wait_full = [&](uint32_t pos) {
         PT_MARK(0)
         const bool r = mbar_wait(BAR(kRFull + stage_of(pos)), (pos / NS) & 1, wctx, 511);
-        PT_MARK(2)
+        if (pos & 1u) { PT_MARK(2) } else { PT_MARK(1) }  // (base is even: odd positions are dO tiles)
         return r;
       };
       auto wait_free = [&]() -> bool {  // the previous item's epilogue has drained the accumulators
@@ -825,6 +832,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           umma_commit_led(BAR(kREmpty + sd), led);
           umma_commit_led(BAR(kYFree), led);
           __syncwarp();
+          PT_MARK(6)
           return true;
         };
         for (int i = 0; i < T && ok; ++i) {
@@ -839,6 +847,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             ++x_issued;
           }
           __syncwarp();
+          PT_MARK(5)
           if (i > 0) {
             ok = issue_dv(i - 1);
             if (!ok) break;
@@ -853,6 +862,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             ++x_issued;
           }
           __syncwarp();
+          PT_MARK(7)
         }
         if (ok) ok = x_ready();  // dP^T of the last tile is in registers, so its P^T is complete
         if (ok) ok = issue_dv(T - 1);
@@ -881,6 +891,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             umma_commit_led(BAR(kYFree), led);
           }
           __syncwarp();
+          PT_MARK(5)
         }
       }
       if (!ok) break;

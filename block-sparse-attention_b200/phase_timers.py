@@ -30,7 +30,7 @@ FWD_PHASES = {
 BWD_ROLES = {
     "dQ compute group 0": 0, "dQ compute group 1": 8, "dQ issuer S": 16, "dQ issuer dQ": 24, "dQ issuer dP": 32,
     "dK/dV compute group 0": 64, "dK/dV compute group 1": 72, "dK/dV issuer 0 (S^T, dP^T, dV)": 80,
-    "dK/dV issuer 1 (dK)": 88,
+    "dK/dV issuer 1 (dK)": 88, "dK/dV producer": 96,
 }
 BWD_PHASES = {
     "dq_compute": ["other", "wait S", "ld S + exp", "wait dP", "ld dP + dS + st", "epilogue", "-", "-"],
@@ -38,7 +38,9 @@ BWD_PHASES = {
                   "-", "-"],
     "dkv_compute": ["other", "wait S^T", "ld S^T + exp", "wait dP^T", "ld dP^T + dS^T + st", "epilogue",
                     "wait Y free", "wait row stats"],
-    "dkv_issuer": ["other + issue", "-", "wait ring", "wait X free", "wait dS^T", "-", "-", "-"],
+    "dkv_issuer": ["other", "wait Q tile", "wait dO tile", "wait X free", "wait dS^T", "issue S^T / dK", "issue dV",
+                   "issue dP^T"],
+    "dkv_producer": ["other + issue", "wait K/V free", "wait stage for Q", "wait stage for dO", "-", "-", "-", "-"],
 }
 
 
@@ -125,6 +127,8 @@ def main():
             return BWD_PHASES["dq_issuer"]
         if n.startswith("dK/dV compute"):
             return BWD_PHASES["dkv_compute"]
+        if n.startswith("dK/dV producer"):
+            return BWD_PHASES["dkv_producer"]
         return BWD_PHASES["dkv_issuer"]
 
     table(f"BF16 backward, {args.workload} ({pairs} pairs)", BWD_ROLES, list(bwd_buf), bwd_phases, per_cta)
