@@ -610,10 +610,11 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 // 3. dK/dV kernel
 // ------------------------------------------------------------------------------------------------
 // smem: K | V | ring of 5 tiles (Q_i, dO_i alternating) | row statistics [2][2][128] f32 | barriers | misc
-// Tensor memory: X @0 takes S^T_i and, once every compute thread holds S^T_i in registers, dP^T_i; once that is
-// in registers too, S^T_{i+1}.  Y @128 takes P^T_i and dS^T_i (bf16, 32 columns each per compute group), the
-// tensor-memory operands of dV @256 += P^T dO and dK @384 += dS^T Q.  No MMA result that iteration i+1 needs waits
-// for an MMA that consumes what the compute threads produce in iteration i.
+// Tensor memory: S @0 takes S^T_i; the next one is issued as soon as every compute thread holds S^T_i in registers,
+// i.e. one tile ahead of the compute threads.  G @128 takes dP^T_i and, once a compute thread holds its 64 columns
+// of it in registers, that thread's P^T_i (bf16, first 32 of its columns) and dS^T_i (last 32): the tensor-memory
+// operands of dV @256 += P^T dO and dK @384 += dS^T Q.  dP^T_{i+1} follows dV_i and dK_i in the issuing thread's
+// program order, so region G needs no barrier of its own.
 constexpr int kDkvStages = 5;
 constexpr int kStatSlots = 2;
 constexpr int kDkvSmem = 2 * kTile + kDkvStages * kTile + kStatSlots * 1024 + BwdSmem::kBarBytes + BwdSmem::kMisc;
@@ -640,10 +641,10 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   }
   const uint32_t bar_base = smem_u32(bars);
   auto BAR = [&](int i) { return bar_base + (uint32_t)i * 8u; };
-  // kv_full, kv_empty, ring_full[NS], ring_empty[NS], s_full, dp_full, x_free, y_free, ds_full, fin, free
-  constexpr int kKvFull = 0, kKvEmpty = 1, kRFull = 2, kREmpty = 2 + NS, kSFull = 2 + 2 * NS, kDpFull = kSFull + 1,
-                kXFree = kDpFull + 1, kYFree = kXFree + 1, kDsFull = kYFree + 1,
-                kFinal = kDsFull + 1, kFree = kFinal + 1, kNumBars = kFree + 1;
+  // kv_full, kv_empty, ring_full[NS], ring_empty[NS], s_full, s_free, dp_full, p_full, ds_full, fin, free
+  constexpr int kKvFull = 0, kKvEmpty = 1, kRFull = 2, kREmpty = 2 + NS, kSFull = 2 + 2 * NS, kSFree = kSFull + 1,
+                kDpFull = kSFree + 1, kPFull = kDpFull + 1, kDsFull = kPFull + 1, kFinal = kDsFull + 1,
+                kFree = kFinal + 1, kNumBars = kFree + 1;
   static_assert(kNumBars <= 32, "barrier slots");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   WaitCtx wctx{&s_abort, p.status};
@@ -657,9 +658,9 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     }
     mbar_init(BAR(kSFull), 1);
     mbar_init(BAR(kDpFull), 1);
-    mbar_init(BAR(kXFree), 256);  // every compute thread holds its part of X (S^T, then dP^T) in registers
-    mbar_init(BAR(kYFree), 2);    // dV_i and dK_i (one commit each) have read P^T_i and dS^T_i from Y
-    mbar_init(BAR(kDsFull), 256);
+    mbar_init(BAR(kSFree), 256);   // every compute thread holds its part of S^T_i in registers
+    mbar_init(BAR(kPFull), 256);   // ... has stored its part of P^T_i
+    mbar_init(BAR(kDsFull), 256);  // ... and of dS^T_i
     mbar_init(BAR(kFinal), 2);
     mbar_init(BAR(kFree), 256);
     mbar_fence_init();
@@ -673,7 +674,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = s_tmem_base;
-  const uint32_t tX = tmem, tY = tmem + 128u, tdV = tmem + 256u, tdK = tmem + 384u;
+  const uint32_t tS = tmem, tG = tmem + 128u, tdV = tmem + 256u, tdK = tmem + 384u;
   const int num_work = p.B * p.H * p.Nkv;
 
   constexpr int kPerIt = 128 / BLK;              // CSR entries per 128-row iteration
@@ -769,19 +770,16 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     PT_MARK(0)
     PTB_FLUSH(64 + 32)
   } else if (warp == kBwdMmaWarp || warp == kBwdMmaWarp + 1) {
-    // Two issuing warps.  The tensor pipe executes MMAs in the order they were issued, whoever issued them, so the
-    // order decides what arrives late:
-    //   issuer 0: everything into X, alternately S^T_i = K Q_i^T and dP^T_i = V dO_i^T, each as soon as every compute
-    //             thread has loaded the previous content of X into registers (x_free); and dV += P^T_{i-1} dO_{i-1}
-    //             right BEHIND S^T_i, so that the dV MMAs never sit in front of the S^T the compute threads wait for
-    //             (P^T_{i-1} is complete by then: a compute thread stores it before it loads dP^T_{i-1}).
-    //   issuer 1: dK += dS^T_i Q_i.
-    // Y goes back to the compute threads when dV_i and dK_i have both completed (y_free, one commit each).
-    // Each issuer visits every ring position in increasing order (a parity wait is never more than one phase
-    // behind) and releases every stage once: by a commit after its last MMA on the tile, or by a plain arrival.
+    // Two issuing warps, one per dependency chain:
+    //   issuer 0: S^T_i = K Q_i^T into region S as soon as every compute thread holds S^T_{i-1} in registers, i.e.
+    //             one tile ahead of the compute threads, whose exponentials therefore never wait for it;
+    //   issuer 1: region G.  dP^T_i = V dO_i^T, then (the compute threads having replaced it by P^T_i and dS^T_i)
+    //             dV += P^T_i dO_i, dK += dS^T_i Q_i and, behind them in program order, dP^T_{i+1}.
+    // Each issuer visits every ring position in increasing order and releases every stage once: by a commit after
+    // its last MMA on the tile, or by a plain arrival for a tile it does not read.
     const int who = warp - kBwdMmaWarp;
     const uint32_t led = lane == 0;  // the whole warp runs the issue code, this lane issues
-    uint32_t r_cnt = 0, kv_cnt = 0, ds_cnt = 0, free_cnt = 0, x_issued = 0, x_waited = 0;
+    uint32_t r_cnt = 0, kv_cnt = 0, in_cnt = 0, ds_cnt = 0, free_cnt = 0;
     bool ok = true, first_item = true;
     const uint64_t k_desc = desc_k_major(smem_u32(sK)), v_desc = desc_k_major(smem_u32(sV));
     const uint64_t ring_k = desc_k_major(smem_u32(sRing)), ring_mn = desc_mn_major(smem_u32(sRing));
@@ -813,85 +811,69 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         return r;
       };
       if (who == 0) {
-        // ---- issuer 0.  Content number n of X (S^T and dP^T alternate) may be written once phases 0..n-1 of
-        // x_free have completed; the phases are waited for one by one, in order.
-        auto x_ready = [&]() -> bool {
-          PT_MARK(0)
-          while (x_waited < x_issued) {
-            if (!mbar_wait(BAR(kXFree), x_waited & 1, wctx, 512)) return false;
-            ++x_waited;
-          }
-          PT_MARK(3)
-          tc_fence_after();
-          return true;
-        };
-        auto issue_dv = [&](int i) -> bool {  // after x_ready() has seen dP^T_i consumed
-          if (i == 0 && !wait_free()) return false;
-          const uint32_t sd = stage_of(base + 2 * i + 1);
-          mma_ts_kmn(tdV, tY, tY + 64u, ring_mn + sd * kTileDescStep, i > 0, led, idesc_n);  // dV += P^T_i dO_i
-          umma_commit_led(BAR(kREmpty + sd), led);
-          umma_commit_led(BAR(kYFree), led);
-          __syncwarp();
-          PT_MARK(6)
-          return true;
-        };
         for (int i = 0; i < T && ok; ++i) {
           ok = wait_full(base + 2 * i);  // Q_i
-          if (ok) ok = x_ready();
+          if (ok && in_cnt > 0) {        // S^T of the tile before (of this or the previous item) is in registers
+            PT_MARK(0)
+            ok = mbar_wait(BAR(kSFree), (in_cnt - 1) & 1, wctx, 512);
+            PT_MARK(3)
+          }
           if (!ok) break;
+          ++in_cnt;
+          tc_fence_after();
           {
             const uint32_t sq = stage_of(base + 2 * i);
-            mma_ss_kk(tX, k_desc, ring_k + sq * kTileDescStep, false, led, ksteps);  // S^T_i
+            mma_ss_kk(tS, k_desc, ring_k + sq * kTileDescStep, false, led, ksteps);  // S^T_i
             umma_commit_led(BAR(kSFull), led);
             umma_commit_led(BAR(kREmpty + sq), led);
-            ++x_issued;
           }
           __syncwarp();
           PT_MARK(5)
-          if (i > 0) {
-            ok = issue_dv(i - 1);
-            if (!ok) break;
-          }
-          ok = wait_full(base + 2 * i + 1);  // dO_i
-          if (ok) ok = x_ready();
-          if (!ok) break;
-          {
-            const uint32_t sd = stage_of(base + 2 * i + 1);
-            mma_ss_kk(tX, v_desc, ring_k + sd * kTileDescStep, false, led, ksteps);  // dP^T_i
-            umma_commit_led(BAR(kDpFull), led);
-            ++x_issued;
-          }
-          __syncwarp();
-          PT_MARK(7)
-        }
-        if (ok) ok = x_ready();  // dP^T of the last tile is in registers, so its P^T is complete
-        if (ok) ok = issue_dv(T - 1);
-      } else {
-        // ---- issuer 1
-        for (int i = 0; i < T && ok; ++i) {
-          ok = wait_full(base + 2 * i);  // Q_i
-          if (ok) ok = wait_full(base + 2 * i + 1);  // dO_i: not read here, released by a plain arrival
+          ok = wait_full(base + 2 * i + 1);  // dO_i: not read here, released by a plain arrival
           if (!ok) break;
           if (led) mbar_arrive(BAR(kREmpty + stage_of(base + 2 * i + 1)));
           __syncwarp();
+        }
+      } else {
+        auto issue_dp = [&](int i) -> bool {
+          if (!wait_full(base + 2 * i)) return false;      // Q_i: read by dK_i later
+          if (!wait_full(base + 2 * i + 1)) return false;  // dO_i
+          const uint32_t sd = stage_of(base + 2 * i + 1);
+          mma_ss_kk(tG, v_desc, ring_k + sd * kTileDescStep, false, led, ksteps);  // dP^T_i
+          umma_commit_led(BAR(kDpFull), led);
+          __syncwarp();
+          PT_MARK(7)
+          return true;
+        };
+        ok = issue_dp(0);
+        for (int i = 0; i < T && ok; ++i) {
           PT_MARK(0)
-          ok = mbar_wait(BAR(kDsFull), ds_cnt & 1, wctx, 514);  // dS^T_i in tensor memory
+          ok = mbar_wait(BAR(kPFull), in_cnt & 1, wctx, 513);  // P^T_i in region G
+          ++in_cnt;
+          PT_MARK(3)
+          if (ok && i == 0) ok = wait_free();
           if (!ok) break;
-          PT_MARK(4)
-          ++ds_cnt;
-          if (i == 0 && !wait_free()) {
-            ok = false;
-            break;
+          tc_fence_after();
+          {
+            const uint32_t sd = stage_of(base + 2 * i + 1);
+            mma_ts_kmn(tdV, tG, tG + 64u, ring_mn + sd * kTileDescStep, i > 0, led, idesc_n);  // dV += P^T_i dO_i
+            umma_commit_led(BAR(kREmpty + sd), led);
           }
+          __syncwarp();
+          PT_MARK(6)
+          ok = mbar_wait(BAR(kDsFull), ds_cnt & 1, wctx, 514);  // dS^T_i in region G
+          ++ds_cnt;
+          PT_MARK(4)
+          if (!ok) break;
           tc_fence_after();
           {
             const uint32_t sq = stage_of(base + 2 * i);
-            mma_ts_kmn(tdK, tY + 32u, tY + 96u, ring_mn + sq * kTileDescStep, i > 0, led, idesc_n);  // dK += dS^T Q_i
+            mma_ts_kmn(tdK, tG + 32u, tG + 96u, ring_mn + sq * kTileDescStep, i > 0, led, idesc_n);  // dK += dS^T_i Q_i
             umma_commit_led(BAR(kREmpty + sq), led);
-            umma_commit_led(BAR(kYFree), led);
           }
           __syncwarp();
           PT_MARK(5)
+          if (i + 1 < T) ok = issue_dp(i + 1);  // over region G: behind dV_i and dK_i in this thread's order
         }
       }
       if (!ok) break;
@@ -910,7 +892,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     const int row = threadIdx.x & 127;  // kv token inside the block = tensor-memory lane
     const bool row_active = (BLK == 128) || (row < 64);  // warp-uniform
     const uint32_t lane_base = (uint32_t)((warp & 3) * 32) << 16;
-    uint32_t s_cnt = 0, dp_cnt = 0, fin_cnt = 0, tile_cnt = 0, r_cnt = 0, y_cnt = 0;
+    uint32_t s_cnt = 0, dp_cnt = 0, fin_cnt = 0, tile_cnt = 0, r_cnt = 0;
     const uint64_t sc2 = pack2(p.scale_log2, p.scale_log2);
     bool ok = true;
     PT_DECL
@@ -952,16 +934,11 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         if (!row_active) {
           // idle half of a 64-token block: barrier protocol only, in exactly the order of the working threads
           // (an arrival for the next phase of a 256-thread barrier must not precede the end of the running one)
-          mbar_arrive(BAR(kXFree));
-          if (y_cnt > 0) {
-            ok = mbar_wait(BAR(kYFree), (y_cnt - 1) & 1, wctx, 524);
-            if (!ok) break;
-          }
-          ++y_cnt;
+          mbar_arrive(BAR(kSFree));
           ok = mbar_wait(BAR(kDpFull), dp_cnt & 1, wctx, 521);
           if (!ok) break;
           ++dp_cnt;
-          mbar_arrive(BAR(kXFree));
+          mbar_arrive(BAR(kPFull));
           mbar_arrive(BAR(kDsFull));
           continue;
         }
@@ -977,13 +954,13 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         float pr[64];
         {
           uint32_t* u = reinterpret_cast<uint32_t*>(pr);
-          tmem_ld32(tX + lane_base + grp * 64, u);
-          tmem_ld32(tX + lane_base + grp * 64 + 32, u + 32);
+          tmem_ld32(tS + lane_base + grp * 64, u);
+          tmem_ld32(tS + lane_base + grp * 64 + 32, u + 32);
           tmem_wait_ld();
         }
-        // S^T_i is in registers: X may take dP^T_i
+        // S^T_i is in registers: region S may take S^T_{i+1}
         tc_fence_before();
-        mbar_arrive(BAR(kXFree));
+        mbar_arrive(BAR(kSFree));
 #pragma unroll
         for (int c4 = 0; c4 < 16; ++c4) {
           const float4 l = st_l[c4];  // negated
@@ -1000,21 +977,6 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
 #pragma unroll
           for (int c = 0; c < 64; ++c) pr[c] = 0.f;
         }
-        // Y still feeds dV / dK of the tile before until their commit
-        PT_MARK(2)
-        if (y_cnt > 0) {
-          ok = mbar_wait(BAR(kYFree), (y_cnt - 1) & 1, wctx, 524);
-          if (!ok) break;
-        }
-        PT_MARK(6)
-        ++y_cnt;
-        tc_fence_after();
-        {
-          uint32_t pk[32];
-#pragma unroll
-          for (int e = 0; e < 32; ++e) pk[e] = pack_bf16x2(pr[2 * e], pr[2 * e + 1]);
-          tmem_st32(tY + lane_base + grp * 64, pk);  // completion is awaited below, under the dP^T load
-        }
         PT_MARK(2)
         // ---- phase 2: dS^T = P^T o (dP^T - delta[q]) -> bf16 -> Y
         ok = mbar_wait(BAR(kDpFull), dp_cnt & 1, wctx, 521);
@@ -1023,14 +985,22 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         ++dp_cnt;
         tc_fence_after();
         uint32_t dp[64];
-        tmem_ld32(tX + lane_base + grp * 64, dp);
-        tmem_ld32(tX + lane_base + grp * 64 + 32, dp + 32);
+        tmem_ld32(tG + lane_base + grp * 64, dp);
+        tmem_ld32(tG + lane_base + grp * 64 + 32, dp + 32);
         tmem_wait_ld();
-        // dP^T_i is in registers: X may take S^T_{i+1}.  P^T must be complete before this thread says so: the
-        // dV MMAs follow this signal.
+        // dP^T_i is in registers: this thread's 64 columns of region G now take P^T_i (bf16, first 32 columns) and
+        // dS^T_i (last 32), the tensor-memory operands of dV and dK
+#pragma unroll
+        for (int h = 0; h < 4; ++h) {  // packed eight registers at a time: pr and dp are both live here
+          uint32_t pk[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) pk[e] = pack_bf16x2(pr[16 * h + 2 * e], pr[16 * h + 2 * e + 1]);
+          tmem_st8(tG + lane_base + grp * 64 + h * 8, pk);
+        }
         tmem_wait_st();
         tc_fence_before();
-        mbar_arrive(BAR(kXFree));
+        mbar_arrive(BAR(kPFull));
+        PT_MARK(6)
         {
           uint32_t pk[32];
 #pragma unroll
@@ -1046,7 +1016,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
             pk[c4 * 2] = pack_bf16x2(d0, d1);
             pk[c4 * 2 + 1] = pack_bf16x2(d2, d3);
           }
-          tmem_st32(tY + lane_base + grp * 64 + 32, pk);
+          tmem_st32(tG + lane_base + grp * 64 + 32, pk);
           tmem_wait_st();
         }
         tc_fence_before();
