@@ -613,8 +613,8 @@ bwd_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ 
 // Tensor memory: S @0 takes S^T_i; the next one is issued as soon as every compute thread holds S^T_i in registers,
 // i.e. one tile ahead of the compute threads.  G @128 takes dP^T_i and, once a compute thread holds its 64 columns
 // of it in registers, that thread's P^T_i (bf16, first 32 of its columns) and dS^T_i (last 32): the tensor-memory
-// operands of dV @256 += P^T dO and dK @384 += dS^T Q.  dP^T_{i+1} follows dV_i and dK_i in the issuing thread's
-// program order, so region G needs no barrier of its own.
+// operands of dV @256 += P^T dO and dK @384 += dS^T Q.  dP^T_{i+1} follows dK_i in the issuing thread's program
+// order and waits for the commit behind dV_i (issued by the other warp).
 constexpr int kDkvStages = 5;
 constexpr int kStatSlots = 2;
 constexpr int kDkvSmem = 2 * kTile + kDkvStages * kTile + kStatSlots * 1024 + BwdSmem::kBarBytes + BwdSmem::kMisc;
@@ -643,8 +643,8 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
   auto BAR = [&](int i) { return bar_base + (uint32_t)i * 8u; };
   // kv_full, kv_empty, ring_full[NS], ring_empty[NS], s_full, s_free, dp_full, p_full, ds_full, fin, free
   constexpr int kKvFull = 0, kKvEmpty = 1, kRFull = 2, kREmpty = 2 + NS, kSFull = 2 + 2 * NS, kSFree = kSFull + 1,
-                kDpFull = kSFree + 1, kPFull = kDpFull + 1, kDsFull = kPFull + 1, kFinal = kDsFull + 1,
-                kFree = kFinal + 1, kNumBars = kFree + 1;
+                kDpFull = kSFree + 1, kPFull = kDpFull + 1, kDsFull = kPFull + 1, kGFree = kDsFull + 1,
+                kFinal = kGFree + 1, kFree = kFinal + 1, kNumBars = kFree + 1;
   static_assert(kNumBars <= 32, "barrier slots");
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   WaitCtx wctx{&s_abort, p.status};
@@ -661,6 +661,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     mbar_init(BAR(kSFree), 256);   // every compute thread holds its part of S^T_i in registers
     mbar_init(BAR(kPFull), 256);   // ... has stored its part of P^T_i
     mbar_init(BAR(kDsFull), 256);  // ... and of dS^T_i
+    mbar_init(BAR(kGFree), 1);     // dV_i has read P^T_i: region G may take dP^T_{i+1} (once dK_i is issued too)
     mbar_init(BAR(kFinal), 2);
     mbar_init(BAR(kFree), 256);
     mbar_fence_init();
@@ -770,13 +771,14 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
     PT_MARK(0)
     PTB_FLUSH(64 + 32)
   } else if (warp == kBwdMmaWarp || warp == kBwdMmaWarp + 1) {
-    // Two issuing warps, one per dependency chain:
+    // Two issuing warps:
     //   issuer 0: S^T_i = K Q_i^T into region S as soon as every compute thread holds S^T_{i-1} in registers, i.e.
-    //             one tile ahead of the compute threads, whose exponentials therefore never wait for it;
-    //   issuer 1: region G.  dP^T_i = V dO_i^T, then (the compute threads having replaced it by P^T_i and dS^T_i)
-    //             dV += P^T_i dO_i, dK += dS^T_i Q_i and, behind them in program order, dP^T_{i+1}.
-    // Each issuer visits every ring position in increasing order and releases every stage once: by a commit after
-    // its last MMA on the tile, or by a plain arrival for a tile it does not read.
+    //             one tile ahead of the compute threads, whose exponentials therefore never wait for it; and
+    //             dV += P^T_i dO_i as soon as P^T_i is stored (nothing waits for dV, so it stays off the other chain);
+    //   issuer 1: the chain through region G.  dP^T_i = V dO_i^T, then (the compute threads having replaced it by
+    //             P^T_i and dS^T_i) dK += dS^T_i Q_i and, behind it in program order and once dV_i has completed
+    //             (g_free), dP^T_{i+1}.
+    // Each issuer releases every ring stage once, by a commit after its last MMA on the tile.
     const int who = warp - kBwdMmaWarp;
     const uint32_t led = lane == 0;  // the whole warp runs the issue code, this lane issues
     uint32_t r_cnt = 0, kv_cnt = 0, in_cnt = 0, ds_cnt = 0, free_cnt = 0;
@@ -811,28 +813,45 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         return r;
       };
       if (who == 0) {
-        for (int i = 0; i < T && ok; ++i) {
-          ok = wait_full(base + 2 * i);  // Q_i
-          if (ok && in_cnt > 0) {        // S^T of the tile before (of this or the previous item) is in registers
+        // S^T_{i+1} as soon as S^T_i is in registers, dV_i as soon as P^T_i is stored
+        auto issue_st = [&](int i) -> bool {
+          if (!wait_full(base + 2 * i)) return false;  // Q_i
+          if (in_cnt > 0) {  // S^T of the tile before (of this or the previous item) is in registers
             PT_MARK(0)
-            ok = mbar_wait(BAR(kSFree), (in_cnt - 1) & 1, wctx, 512);
+            const bool r = mbar_wait(BAR(kSFree), (in_cnt - 1) & 1, wctx, 512);
             PT_MARK(3)
+            if (!r) return false;
           }
-          if (!ok) break;
           ++in_cnt;
           tc_fence_after();
-          {
-            const uint32_t sq = stage_of(base + 2 * i);
-            mma_ss_kk(tS, k_desc, ring_k + sq * kTileDescStep, false, led, ksteps);  // S^T_i
-            umma_commit_led(BAR(kSFull), led);
-            umma_commit_led(BAR(kREmpty + sq), led);
-          }
+          const uint32_t sq = stage_of(base + 2 * i);
+          mma_ss_kk(tS, k_desc, ring_k + sq * kTileDescStep, false, led, ksteps);  // S^T_i
+          umma_commit_led(BAR(kSFull), led);
+          umma_commit_led(BAR(kREmpty + sq), led);
           __syncwarp();
           PT_MARK(5)
-          ok = wait_full(base + 2 * i + 1);  // dO_i: not read here, released by a plain arrival
+          return true;
+        };
+        ok = issue_st(0);
+        for (int i = 0; i < T && ok; ++i) {
+          if (i + 1 < T) ok = issue_st(i + 1);
+          if (ok) ok = wait_full(base + 2 * i + 1);  // dO_i
           if (!ok) break;
-          if (led) mbar_arrive(BAR(kREmpty + stage_of(base + 2 * i + 1)));
+          PT_MARK(0)
+          ok = mbar_wait(BAR(kPFull), ds_cnt & 1, wctx, 513);  // P^T_i in region G
+          ++ds_cnt;
+          PT_MARK(4)
+          if (ok && i == 0) ok = wait_free();
+          if (!ok) break;
+          tc_fence_after();
+          {
+            const uint32_t sd = stage_of(base + 2 * i + 1);
+            mma_ts_kmn(tdV, tG, tG + 64u, ring_mn + sd * kTileDescStep, i > 0, led, idesc_n);  // dV += P^T_i dO_i
+            umma_commit_led(BAR(kREmpty + sd), led);
+            umma_commit_led(BAR(kGFree), led);
+          }
           __syncwarp();
+          PT_MARK(6)
         }
       } else {
         auto issue_dp = [&](int i) -> bool {
@@ -841,6 +860,7 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           const uint32_t sd = stage_of(base + 2 * i + 1);
           mma_ss_kk(tG, v_desc, ring_k + sd * kTileDescStep, false, led, ksteps);  // dP^T_i
           umma_commit_led(BAR(kDpFull), led);
+          umma_commit_led(BAR(kREmpty + sd), led);
           __syncwarp();
           PT_MARK(7)
           return true;
@@ -848,22 +868,10 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
         ok = issue_dp(0);
         for (int i = 0; i < T && ok; ++i) {
           PT_MARK(0)
-          ok = mbar_wait(BAR(kPFull), in_cnt & 1, wctx, 513);  // P^T_i in region G
-          ++in_cnt;
-          PT_MARK(3)
-          if (ok && i == 0) ok = wait_free();
-          if (!ok) break;
-          tc_fence_after();
-          {
-            const uint32_t sd = stage_of(base + 2 * i + 1);
-            mma_ts_kmn(tdV, tG, tG + 64u, ring_mn + sd * kTileDescStep, i > 0, led, idesc_n);  // dV += P^T_i dO_i
-            umma_commit_led(BAR(kREmpty + sd), led);
-          }
-          __syncwarp();
-          PT_MARK(6)
           ok = mbar_wait(BAR(kDsFull), ds_cnt & 1, wctx, 514);  // dS^T_i in region G
           ++ds_cnt;
           PT_MARK(4)
+          if (ok && i == 0) ok = wait_free();
           if (!ok) break;
           tc_fence_after();
           {
@@ -873,7 +881,11 @@ bwd_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__
           }
           __syncwarp();
           PT_MARK(5)
-          if (i + 1 < T) ok = issue_dp(i + 1);  // over region G: behind dV_i and dK_i in this thread's order
+          // dV_i (issued by the other warp when P^T_i was stored) has read region G as well
+          ok = mbar_wait(BAR(kGFree), in_cnt & 1, wctx, 516);
+          ++in_cnt;
+          PT_MARK(3)
+          if (ok && i + 1 < T) ok = issue_dp(i + 1);
         }
       }
       if (!ok) break;

@@ -29,8 +29,8 @@ FWD_PHASES = {
 }
 BWD_ROLES = {
     "dQ compute group 0": 0, "dQ compute group 1": 8, "dQ issuer S": 16, "dQ issuer dQ": 24, "dQ issuer dP": 32,
-    "dK/dV compute group 0": 64, "dK/dV compute group 1": 72, "dK/dV issuer 0 (S^T)": 80,
-    "dK/dV issuer 1 (dP^T, dV, dK)": 88, "dK/dV producer": 96,
+    "dK/dV compute group 0": 64, "dK/dV compute group 1": 72, "dK/dV issuer 0 (S^T, dV)": 80,
+    "dK/dV issuer 1 (dP^T, dK)": 88, "dK/dV producer": 96,
 }
 BWD_PHASES = {
     "dq_compute": ["other", "wait S", "ld S + exp", "wait dP", "ld dP + dS + st", "epilogue", "-", "-"],
@@ -38,7 +38,7 @@ BWD_PHASES = {
                   "-", "-"],
     "dkv_compute": ["other", "wait S^T", "ld S^T + exp", "wait dP^T", "dS^T + st", "epilogue",
                     "ld dP^T + P^T st", "wait row stats"],
-    "dkv_issuer": ["other", "wait Q tile", "wait dO tile", "wait S free / P^T", "wait dS^T", "issue S^T / dK", "issue dV",
+    "dkv_issuer": ["other", "wait Q tile", "wait dO tile", "wait S free / dV done", "wait P^T / dS^T", "issue S^T / dK", "issue dV",
                    "issue dP^T"],
     "dkv_producer": ["other + issue", "wait K/V free", "wait stage for Q", "wait stage for dO", "-", "-", "-", "-"],
 }
