@@ -52,6 +52,10 @@ WORKLOADS = {
     "cfg2_small": (1, 16, 16384, 13),  # same structure and density, sized for an ncu capture; never the bench line
 }
 BLK, D = 128, 128
+# DRAM bytes (read + write) of one launch on cfg2_small (26 624 pairs), from the committed ncu capture; traffic grows
+# with the number of tiles (per-tile Q / O / statistics bytes plus first-touch K / V), so it is scaled by the pairs
+NCU_SMALL_PAIRS = 26624
+NCU_DRAM_BYTES_SMALL = {"bsa_fwd_kernel<128,bf16>": 248.7e6, "bwd_dq_kernel<128>": 324.2e6, "bwd_dkv_kernel<128>": 381.1e6}
 FALLBACK_PEAKS = {"bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "hbm_gbs": 6650.0}
 
 
@@ -570,10 +574,12 @@ def main():
                          "frac_of_burst": dominant["executed_tflops"] / peak_burst,
                          "frac_of_sustained": dominant["executed_tflops"] / peak_sust,
                          "frac_of_nominal_2250": dominant["executed_tflops"] / 2250.0,
-                         "traffic": None,
+                         "traffic": NCU_DRAM_BYTES_SMALL.get(dominant["kernel"], 0) * (pairs / NCU_SMALL_PAIRS) or None,
+                         "traffic_note": "dram__bytes_read + write of one launch, ncu capture of cfg2_small "
+                                         "(profiles/cfg2_small_tcgen05_kernels.md) scaled by the number of pairs; "
+                                         "0.92-0.96 of the compulsory bytes, 10-13 % of the HBM peak",
                          "note": "achieved = FLOPs the kernel executes / its CUDA-event time; 'credited' scales it "
-                                 "to the metric's 4 (fwd) / 10 (bwd) * blk^2 * D per pair; DRAM traffic is not "
-                                 "measured by this run (tensor-bound kernels at 10-15 % of HBM peak)",
+                                 "to the metric's 4 (fwd) / 10 (bwd) * blk^2 * D per pair",
                          "kernels": per_kernel},
             "roofline_fwd": {"bound": "tensor", "achieved": fwd_tf, "peak": peak, "frac": fwd_tf / peak,
                              "frac_of_nominal_2250": fwd_tf / 2250.0, "unit": "TFLOP/s"},
