@@ -526,15 +526,12 @@ def main():
         peak_burst = float(peaks.get("bf16_tflops") or FALLBACK_PEAKS["bf16_tflops"])
         peak_sust = float(peaks.get("bf16_tflops_sustained") or peak_burst)
         hbm_peak = float(peaks.get("hbm_gbs") or FALLBACK_PEAKS["hbm_gbs"])
-        # The denominator follows the clocks seen during the timed region: when the power cap was active (it
-        # engages within about ten launches of these kernels: 770-990 W, SMs at 1.56-1.67 of 1.965 GHz) or the
-        # region lasted a second or more, the sustained (power-capped) GEMM figure, else the burst one.  Both
-        # fractions are in the line.
+        # a timed region of less than a second is compared with the burst GEMM figure, a longer one with the
+        # sustained one; both fractions are in the line.  (The power cap is active within about ten launches of
+        # these kernels - see `clocks` - so the burst figure is the stricter of the two here.)
         timed_s = total_ms * 1e-3
-        capped = "sw_power_cap" in (clocks or {}).get("reasons", [])
-        sustained = capped or timed_s >= 1.0
-        peak = peak_sust if sustained else peak_burst
-        peak_name = ("sustained, power cap active" if capped else "sustained") if sustained else "burst"
+        peak = peak_burst if timed_s < 1.0 else peak_sust
+        peak_name = "burst" if timed_s < 1.0 else "sustained"
         step_flops = flops_f + (0 if args.fwd_only else flops_b)
         value = world * step_flops / (ms_per_step * 1e-3) / 1e12
         fwd_tf = flops_f / (fwd_ms * 1e-3) / 1e12
@@ -574,10 +571,12 @@ def main():
                          "frac_of_burst": dominant["executed_tflops"] / peak_burst,
                          "frac_of_sustained": dominant["executed_tflops"] / peak_sust,
                          "frac_of_nominal_2250": dominant["executed_tflops"] / 2250.0,
-                         "traffic": NCU_DRAM_BYTES_SMALL.get(dominant["kernel"], 0) * (pairs / NCU_SMALL_PAIRS) or None,
-                         "traffic_note": "dram__bytes_read + write of one launch, ncu capture of cfg2_small "
-                                         "(profiles/cfg2_small_tcgen05_kernels.md) scaled by the number of pairs; "
-                                         "0.92-0.96 of the compulsory bytes, 10-13 % of the HBM peak",
+                         "traffic": None,
+                         "traffic_from_profile": {
+                             "bytes_per_launch_scaled": NCU_DRAM_BYTES_SMALL.get(dominant["kernel"], 0) * (pairs / NCU_SMALL_PAIRS),
+                             "file": "profiles/cfg2_small_tcgen05_kernels.md",
+                             "how": "dram__bytes_read + write of one launch in the ncu capture of cfg2_small, scaled "
+                                    "by the number of pairs; not measured by this run"},
                          "note": "achieved = FLOPs the kernel executes / its CUDA-event time; 'credited' scales it "
                                  "to the metric's 4 (fwd) / 10 (bwd) * blk^2 * D per pair",
                          "kernels": per_kernel},
