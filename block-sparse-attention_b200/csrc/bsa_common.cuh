@@ -53,14 +53,6 @@ __device__ __forceinline__ uint64_t globaltimer_ns() {
   return t;
 }
 
-__device__ __forceinline__ bool elect_one() {
-  uint32_t pred;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\telect.sync _|p, 0xffffffff;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(pred));
-  return pred != 0;
-}
-
 // ---------------------------------------------------------------------------------------------
 // mbarrier
 // ---------------------------------------------------------------------------------------------
@@ -142,77 +134,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const W
   return mbar_wait_limit(bar, parity, ctx, site, BSA_WAIT_LIMIT_NS);
 }
 
-// Non-blocking test of a phase (mbarrier.test_wait never suspends the thread).
-__device__ __forceinline__ bool mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-
-// Same contract as mbar_wait, but polls instead of letting the hardware suspend the thread: the wake-up
-// after a suspended try_wait costs a few hundred clocks, which a role on the critical path (an MMA
-// issuer) cannot hide.  The abort flag and the time limit are checked every 64 polls.
-__device__ __forceinline__ bool mbar_wait_poll(uint32_t bar, uint32_t parity, const WaitCtx& ctx, int site) {
-  bool done = mbar_test_wait(bar, parity);
-  if (!done) {
-    const uint64_t t0 = globaltimer_ns();
-    uint32_t polls = 0;
-    for (;;) {
-      if (mbar_test_wait(bar, parity)) {
-        done = true;
-        break;
-      }
-      if ((++polls & 63u) != 0) continue;
-      if (*ctx.abort_flag) break;
-      if (globaltimer_ns() - t0 > BSA_WAIT_LIMIT_NS) {
-        *ctx.abort_flag = 1;
-        if (atomicCAS(ctx.status, 0, (int)kStatusWaitTimeout) == 0) {
-          ctx.status[1] = (int)blockIdx.x;
-          ctx.status[2] = site;
-          ctx.status[3] = (int)threadIdx.x;
-        }
-        __threadfence();
-        break;
-      }
-    }
-  }
-  return __all_sync(0xffffffffu, done);
-}
-
-// Rendezvous of `count` threads through an mbarrier initialised with that count: arrive, then a
-// bounded wait.  Unlike bar.sync it cannot strand the threads that are already waiting when another
-// role aborts.  `phase_cnt` counts the uses of this barrier by the calling thread.
-__device__ __forceinline__ bool mbar_rendezvous(uint32_t bar, uint32_t& phase_cnt, const WaitCtx& ctx,
-                                                int site) {
-  mbar_arrive(bar);
-  const bool ok = mbar_wait(bar, phase_cnt & 1, ctx, site);
-  ++phase_cnt;
-  return ok;
-}
-
-// Rendezvous for short, rare meeting points (a tile epilogue): polls, so the last arrival is seen within
-// tens of clocks instead of the few hundred a suspended wait needs to wake up.
-__device__ __forceinline__ bool mbar_rendezvous_poll(uint32_t bar, uint32_t& phase_cnt, const WaitCtx& ctx,
-                                                     int site) {
-  mbar_arrive(bar);
-  const bool ok = mbar_wait_poll(bar, phase_cnt & 1, ctx, site);
-  ++phase_cnt;
-  return ok;
-}
-
-// ---------------------------------------------------------------------------------------------
-// named barriers (unaligned forms: safe from divergent warp roles)
-// ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ void named_bar_sync(int id, int nthreads) {
-  asm volatile("barrier.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
-}
-
 // ---------------------------------------------------------------------------------------------
 // fences
 // ---------------------------------------------------------------------------------------------
@@ -248,31 +169,6 @@ __device__ __forceinline__ void tma_load_5d(uint32_t dst, const CUtensorMap* m, 
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(m)), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3),
       "r"(c4)
       : "memory");
-}
-__device__ __forceinline__ void tma_store_5d(const CUtensorMap* m, uint32_t src, int c0, int c1,
-                                             int c2, int c3, int c4) {
-  asm volatile(
-      "cp.async.bulk.tensor.5d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5, %6}], [%1];"
-      ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(c4)
-      : "memory");
-}
-__device__ __forceinline__ void tma_store_4d(const CUtensorMap* m, uint32_t src, int c0, int c1,
-                                             int c2, int c3) {
-  asm volatile(
-      "cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
-      ::"l"(reinterpret_cast<uint64_t>(m)), "r"(src), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
-      : "memory");
-}
-__device__ __forceinline__ void tma_store_commit() {
-  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-}
-template <int N>
-__device__ __forceinline__ void tma_store_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-template <int N>
-__device__ __forceinline__ void tma_store_wait_all() {
-  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -370,43 +266,12 @@ __host__ __device__ constexpr uint32_t umma_idesc(uint32_t a_fmt, uint32_t b_fmt
          ((m >> 4) << 24);
 }
 
-// D[tmem] (+)= A[smem] * B[smem]; kind::f16 (bf16/f16 inputs, f32 accumulate)
-__device__ __forceinline__ void umma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                            uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// D[tmem] (+)= A[tmem] * B[smem]
-__device__ __forceinline__ void umma_f16_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
-                                            uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_f8_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                           uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-__device__ __forceinline__ void umma_f8_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc,
-                                           uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], [%1], %2, %3, p;\n\t}"
-      ::"r"(d_tmem), "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Warp-convergent forms: all 32 lanes execute the statement and only the lane with `leader` != 0 issues.
-// The operands are then computed by convergent code, which lets the compiler keep the descriptors in
-// uniform registers instead of moving them there before every MMA inside a divergent branch.
+// D[tmem] (+)= A * B with A from shared memory (`_ss`) or tensor memory (`_ts`); kind::f16 takes bf16 / f16 inputs,
+// kind::f8f6f4 e4m3, all with f32 accumulation.  Warp-convergent forms: all 32 lanes execute the statement and
+// only the lane with `leader` != 0 issues.  The operands are then computed by convergent code, which lets the
+// compiler keep the descriptors in uniform registers; inside the kernels this measured faster than issuing from a
+// one-lane branch.  The commit makes an mbarrier arrive (count 1) once every MMA the thread issued before it has
+// completed.
 __device__ __forceinline__ void umma_f16_ss_led(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
                                                 uint32_t accumulate, uint32_t leader) {
   asm volatile(
@@ -445,12 +310,6 @@ __device__ __forceinline__ void umma_commit_led(uint32_t bar, uint32_t leader) {
       "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}"
       ::"r"(bar), "r"(leader)
       : "memory");
-}
-// mbarrier arrives (count 1) once every previously issued MMA of this thread has completed.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   bar)
-               : "memory");
 }
 
 // ---------------------------------------------------------------------------------------------
