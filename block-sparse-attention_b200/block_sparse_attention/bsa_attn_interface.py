@@ -752,7 +752,7 @@ def _bsa_attn_bwd(dout, q, k, v, out, lse, q2k_block_index, block_sparse_num, bl
     if block_sizes is not None:
         assert block_sizes.dtype == torch.int32 and block_sizes.device == device
         block_sizes = block_sizes.contiguous()
-    bs_strides = _block_size_strides(block_sizes, B, H, Nkv, (1, 2))
+    bs_strides = _block_size_strides(block_sizes, B, H, Nkv, (1, 2, 3))
     assert q2k_block_index.dtype == torch.int32
     assert q2k_block_index.shape[:3] == (B, H, Nq), (
         f"q2k_block_index has shape {tuple(q2k_block_index.shape)}, expected (b={B}, h={H}, num_q_blocks={Nq}, "

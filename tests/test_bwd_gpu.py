@@ -202,6 +202,20 @@ def test_128_token_blocks_honour_block_sizes_like_the_forward():
     _check(got, q, k, v, do, bias, 1 / math.sqrt(128))
 
 
+def test_128_token_blocks_per_head_block_sizes():
+    """rank 3 (batch, head, kv blocks), as every forward entry accepts it: each (batch, head) slice masks its own
+    tokens, checked slice by slice against the dense reference with that slice's sizes."""
+    q, k, v, do, index, nums = _case(13, 2, 2, 384, 512, [2, 3, 1, 4], poison=False)
+    gen = torch.Generator().manual_seed(61)
+    sizes = torch.randint(1, 129, (2, 2, 4), generator=gen, dtype=torch.int32)
+    got = _run(q, k, v, do, index, 0, nums=nums, sizes=sizes)
+    for bi in range(2):
+        for hi in range(2):
+            sl = (slice(bi, bi + 1), slice(hi, hi + 1))
+            bias = orc.block_sparse_to_attn_bias(index[sl], 0, sizes[bi, hi], 384, 512, q2k_block_nums=nums[sl])
+            _check(tuple(t[sl] for t in got), q[sl], k[sl], v[sl], do[sl], bias, 1 / math.sqrt(128))
+
+
 def test_head_dimension_64_with_128_token_blocks():
     """D = 64 backward exists on the 128-token path only (bsa_attn_interface.py:3867-3873)."""
     from block_sparse_attention import bsa_attn_bwd, bsa_attn_fwd
